@@ -1,0 +1,361 @@
+// Dense W8A8 GEMM for sm_100a: out = epilogue( A(M,K) s8 * B(N,K)^T s8 -> s32 ).
+//
+// One persistent CTA per SM walks 128 x block_n output tiles.  Roles by warp:
+//   warp 0      TMA producer: A (128 x 128 B) and B (block_n x 128 B) boxes, 128-byte swizzle,
+//               into a ring of shared-memory stages, signalled through "full" mbarriers.
+//   warp 1      owns tensor memory; one elected thread issues tcgen05.mma kind::i8
+//               (128 x block_n x 32 per instruction, int32 accumulators in tensor memory) and
+//               commits each stage back to its "empty" mbarrier.
+//   warps 2-5   epilogue: tcgen05.ld the accumulators (one output row per thread),
+//               acc * (act_scale[m] * w_scale[n]) + bias[n], optional GELU / GEGLU, pack to
+//               bf16 / fp16 (or raw int32) and store.
+// Two accumulator buffers in tensor memory let the epilogue of tile i overlap the MMAs of
+// tile i+1.  Every wait is bounded; a wait that runs out records a code in the device
+// status word and all roles fall through to the common teardown.
+#include "common.cuh"
+
+namespace hy3d {
+// Host-side helpers implemented in capi.cu.
+int encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
+                      uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, int swizzle_bytes);
+int device_sm_count();
+int current_device();
+
+namespace dense {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kBlockKBytes = 128;   // one 128-byte swizzle row of int8 = 128 K elements
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kSmemLimit = 227 * 1024;
+
+struct DenseArgs {
+  const float* act_scale;
+  const void* w_scale;
+  const void* bias;
+  void* out;
+  int ws_dtype, bias_dtype, out_dtype, epilogue;
+  int M, N, K;
+  int block_n, stages, acc_cols;
+  int m_tiles, n_tiles, num_kb, last_ksteps;
+};
+
+struct __align__(8) DenseCtrl {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float ws[2][256];
+  float bs[2][256];
+};
+
+__device__ __forceinline__ void epi_bar_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                  const DenseArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  const uint32_t a_bytes = kTileM * kBlockKBytes;
+  const uint32_t b_bytes = static_cast<uint32_t>(p.block_n) * kBlockKBytes;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+  DenseCtrl* ctrl = reinterpret_cast<DenseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kEpiThreads);
+    }
+    ctrl->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_1cta(smem_u32(&ctrl->tmem_base), static_cast<uint32_t>(2 * p.acc_cols));
+    tmem_relinquish_1cta();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const int m0 = (tile % p.m_tiles) * kTileM;
+      const int n0 = (tile / p.m_tiles) * p.block_n;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full = smem_u32(&ctrl->full[stage]);
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          mbar_arrive_expect_tx(full, stage_bytes);
+          tma_load_2d(sa, &tm_a, full, kb * kBlockKBytes, m0);
+          tma_load_2d(sa + a_bytes, &tm_b, full, kb * kBlockKBytes, n0);
+        }
+        __syncwarp();
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    const uint32_t idesc = make_idesc_i8(kTileM, static_cast<uint32_t>(p.block_n), false);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
+                     kDevTimeoutTmemEmpty);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.acc_cols);
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, kDevTimeoutFull);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint64_t da = make_smem_desc(sa, 1024, 128);
+          const uint64_t db = make_smem_desc(sa + a_bytes, 1024, 128);
+          const int nk = (kb == p.num_kb - 1) ? p.last_ksteps : 4;
+          for (int k = 0; k < nk; ++k) {
+            // Each K step of 32 int8 is 32 bytes further along the swizzled row: +2 in the
+            // descriptor's 16-byte address units.
+            mma_i8_1cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
+        }
+        __syncwarp();
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+      if (ok && lane == 0) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
+      __syncwarp();
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int quarter = warp & 3;            // tensor-memory lane quarter this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    const int et = threadIdx.x - 64;         // 0..127
+    const bool geglu = p.epilogue == HY3D_EPI_GEGLU;
+    const int64_t ldo = geglu ? (p.N >> 1) : p.N;
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (tile % p.m_tiles) * kTileM;
+      const int n0 = (tile / p.m_tiles) * p.block_n;
+      if (p.out_dtype != HY3D_S32) {
+        for (int c = et; c < p.block_n; c += kEpiThreads) {
+          const int n = n0 + c;
+          ctrl->ws[buf][c] = n < p.N ? load_scalar(p.w_scale, p.ws_dtype, n) : 0.0f;
+          ctrl->bs[buf][c] = (p.bias && n < p.N) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
+        }
+      }
+      epi_bar_sync();
+      if (ok) ok = mbar_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag,
+                             kDevTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) continue;   // warp-uniform; keeps the named-barrier participation count intact
+      tc_fence_after_sync();
+      const int m = m0 + row_in_tile;
+      const bool row_ok = m < p.M;
+      const float as = (row_ok && p.out_dtype != HY3D_S32) ? p.act_scale[m] : 0.0f;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(buf * p.acc_cols);
+      if (!geglu) {
+        for (int c = 0; c < p.block_n; c += 16) {
+          uint32_t r[16];
+          __syncwarp();
+          tmem_ld_x16(t_row + c, r);
+          tmem_ld_wait();
+          const int n = n0 + c;
+          if (!row_ok || n >= p.N) {
+            // nothing to store for this row / column block
+          } else if (p.out_dtype == HY3D_S32) {
+            int4* dst = reinterpret_cast<int4*>(reinterpret_cast<int32_t*>(p.out) +
+                                                static_cast<int64_t>(m) * ldo + n);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              dst[j] = make_int4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          } else {
+            float y[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              y[j] = fmaf(static_cast<float>(static_cast<int32_t>(r[j])), as * ctrl->ws[buf][c + j],
+                          ctrl->bs[buf][c + j]);
+              if (p.epilogue == HY3D_EPI_GELU) y[j] = gelu_erf(y[j]);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) +
+                                                  static_cast<int64_t>(m) * ldo + n);
+            dst[0] = make_uint4(pack2(y[0], y[1], p.out_dtype), pack2(y[2], y[3], p.out_dtype),
+                                pack2(y[4], y[5], p.out_dtype), pack2(y[6], y[7], p.out_dtype));
+            dst[1] = make_uint4(pack2(y[8], y[9], p.out_dtype), pack2(y[10], y[11], p.out_dtype),
+                                pack2(y[12], y[13], p.out_dtype), pack2(y[14], y[15], p.out_dtype));
+          }
+        }
+      } else {
+        // Columns come in blocks of 32: 16 "value" columns then their 16 "gate" columns.
+        for (int c = 0; c < p.block_n; c += 32) {
+          uint32_t rv[16], rg[16];
+          __syncwarp();
+          tmem_ld_x16(t_row + c, rv);
+          tmem_ld_x16(t_row + c + 16, rg);
+          tmem_ld_wait();
+          const int n = n0 + c;
+          if (row_ok && n < p.N) {
+            float y[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float v = fmaf(static_cast<float>(static_cast<int32_t>(rv[j])),
+                                   as * ctrl->ws[buf][c + j], ctrl->bs[buf][c + j]);
+              const float g = fmaf(static_cast<float>(static_cast<int32_t>(rg[j])),
+                                   as * ctrl->ws[buf][c + 16 + j], ctrl->bs[buf][c + 16 + j]);
+              y[j] = v * gelu_erf(g);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) +
+                                                  static_cast<int64_t>(m) * ldo + (n >> 1));
+            dst[0] = make_uint4(pack2(y[0], y[1], p.out_dtype), pack2(y[2], y[3], p.out_dtype),
+                                pack2(y[4], y[5], p.out_dtype), pack2(y[6], y[7], p.out_dtype));
+            dst[1] = make_uint4(pack2(y[8], y[9], p.out_dtype), pack2(y[10], y[11], p.out_dtype),
+                                pack2(y[12], y[13], p.out_dtype), pack2(y[14], y[15], p.out_dtype));
+          }
+        }
+      }
+      __syncwarp();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // Let copies that may still be in flight land before the shared memory is released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) { }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_1cta(tmem_base, static_cast<uint32_t>(2 * p.acc_cols));
+  }
+}
+
+}  // namespace
+
+
+int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale,
+               int ws_dtype, const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M,
+               int64_t N, int64_t K, int epilogue, int cta_group, int block_n,
+               cudaStream_t stream) {
+  if (!A || !B || !out) return HY3D_ERR_ARG;
+  if (out_dtype != HY3D_F16 && out_dtype != HY3D_BF16 && out_dtype != HY3D_S32) return HY3D_ERR_ARG;
+  if (out_dtype != HY3D_S32 && (!act_scale || !w_scale)) return HY3D_ERR_ARG;
+  if (epilogue < HY3D_EPI_LINEAR || epilogue > HY3D_EPI_GEGLU) return HY3D_ERR_ARG;
+  if (out_dtype == HY3D_S32 && epilogue != HY3D_EPI_LINEAR) return HY3D_ERR_ARG;
+  if (ws_dtype < HY3D_F16 || ws_dtype > HY3D_F32) return HY3D_ERR_ARG;
+  if (bias && (bias_dtype < HY3D_F16 || bias_dtype > HY3D_F32)) return HY3D_ERR_ARG;
+  if (cta_group < 0 || cta_group > 2) return HY3D_ERR_ARG;
+  if (M < 0 || N <= 0 || K <= 0 || (K & 15) || (N & 15)) return HY3D_ERR_SHAPE;
+  if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return HY3D_ERR_SHAPE;
+  const bool geglu = epilogue == HY3D_EPI_GEGLU;
+  if (geglu && (N & 31)) return HY3D_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return HY3D_ERR_SHAPE;
+  if (M == 0) return HY3D_OK;
+
+  if (block_n == 0) {
+    // Widest tile that divides N evenly; otherwise the widest one (ragged last tile).
+    block_n = N >= 256 ? 256 : static_cast<int>(N);
+    for (int bn = 256; bn >= 128; bn -= 16) {
+      if (N % bn == 0) { block_n = bn; break; }
+    }
+    if (N < 256) block_n = static_cast<int>(N);
+  }
+  if (block_n < 16 || block_n > 256 || (block_n & 15) || (geglu && (block_n & 31)))
+    return HY3D_ERR_SHAPE;
+
+  DenseArgs p;
+  p.act_scale = act_scale; p.w_scale = w_scale; p.bias = bias; p.out = out;
+  p.ws_dtype = ws_dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype; p.epilogue = epilogue;
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.block_n = block_n;
+  int acc_cols = 32;
+  while (acc_cols < block_n) acc_cols <<= 1;
+  p.acc_cols = acc_cols;
+  p.m_tiles = static_cast<int>((M + kTileM - 1) / kTileM);
+  p.n_tiles = static_cast<int>((N + block_n - 1) / block_n);
+  p.num_kb = static_cast<int>((K + kBlockKBytes - 1) / kBlockKBytes);
+  const int k_last = static_cast<int>(K - static_cast<int64_t>(p.num_kb - 1) * kBlockKBytes);
+  p.last_ksteps = (k_last + 31) / 32;
+  const int stage_bytes = kTileM * kBlockKBytes + block_n * kBlockKBytes;
+  const int fixed = static_cast<int>(sizeof(DenseCtrl)) + 1024;
+  int stages = (kSmemLimit - fixed) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return HY3D_ERR_SHAPE;
+  p.stages = stages;
+  const int smem_bytes = stages * stage_bytes + fixed;
+
+  CUtensorMap tm_a, tm_b;
+  int rc = encode_tmap_2d_u8(&tm_a, A, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
+                             static_cast<uint64_t>(K), kBlockKBytes, kTileM, 128);
+  if (rc != HY3D_OK) return rc;
+  rc = encode_tmap_2d_u8(&tm_b, B, static_cast<uint64_t>(K), static_cast<uint64_t>(N),
+                         static_cast<uint64_t>(K), kBlockKBytes, static_cast<uint32_t>(block_n), 128);
+  if (rc != HY3D_OK) return rc;
+
+  static bool attr_set[64] = {};
+  const int dev = current_device();
+  if (dev < 0 || dev >= 64) return HY3D_ERR_CUDA;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemLimit) != cudaSuccess)
+      return HY3D_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  const int sms = device_sm_count();
+  if (sms <= 0) return HY3D_ERR_CUDA;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int grid = total_tiles < sms ? total_tiles : sms;
+  gemm_dense_kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_a, tm_b, p);
+  return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
+}
+
+}  // namespace dense
+
+using dense::gemm_dense;
+
+}  // namespace hy3d

@@ -1,0 +1,346 @@
+// 2:4 structured-sparse W8A8 GEMM for sm_100a:
+//     out(M tokens, N) = epilogue( X(M,K) s8 * Wpruned(N,K)^T -> s32 )
+// The pruned weight is the sparse A operand of tcgen05.mma.sp kind::i8 (128 weight rows per
+// tile on the 128 tensor-memory lanes); a block of tokens is the dense B operand, so the
+// accumulator tile is D[weight row, token] and the epilogue writes it transposed.
+//
+// Per 128-deep K block a stage of shared memory holds
+//     A  128 rows x 64 B   compressed weights, 64-byte swizzle      (TMA)
+//     E  128 rows x 16 B   metadata, 8 nibbles per 32 K, plain rows  (TMA, no swizzle)
+//     B  block_t rows x 128 B  int8 activations, 128-byte swizzle   (TMA)
+// The MMA thread copies E into tensor memory with tcgen05.cp (128 lanes x 128 bits = the
+// metadata of two K=64 instructions) and issues two tcgen05.mma.sp per stage.  tcgen05.cp and
+// tcgen05.mma issued by one thread execute in issue order, so one 4-column metadata slot in
+// tensor memory is enough.  Roles, accumulator double-buffering and bounded waits are as in
+// the dense kernel.
+#include "common.cuh"
+
+namespace hy3d {
+namespace sparse {
+namespace {
+
+constexpr int kTileW = 128;          // weight rows per tile (tensor-memory lanes)
+constexpr int kBlockK = 128;         // logical K per stage
+constexpr int kABytes = kTileW * (kBlockK / 2);   // 8192
+constexpr int kEBytes = kTileW * (kBlockK / 8);   // 2048
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kSmemLimit = 227 * 1024;
+constexpr int kMaxBlockT = 240;      // 2 * 240 accumulator columns + 4 metadata columns <= 512
+
+struct SparseArgs {
+  const float* act_scale;
+  const void* w_scale;
+  const void* bias;
+  void* out;
+  int ws_dtype, bias_dtype, out_dtype, epilogue;
+  int M, N, K;
+  int block_t, stages;
+  int w_tiles, t_tiles, num_kb, last_ksteps;
+};
+
+struct __align__(8) SparseCtrl {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float as[2][256];
+};
+
+__device__ __forceinline__ void epi_bar_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+}
+
+__device__ __forceinline__ void store_one(void* out, int out_dtype, int64_t idx, float v) {
+  if (out_dtype == HY3D_BF16)
+    reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+  else
+    reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_e,
+                   const __grid_constant__ CUtensorMap tm_x, const SparseArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  const uint32_t b_bytes = static_cast<uint32_t>(p.block_t) * 128u;
+  const uint32_t stage_bytes = kABytes + kEBytes + b_bytes;
+  SparseCtrl* ctrl = reinterpret_cast<SparseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.w_tiles * p.t_tiles;
+  const uint32_t tmem_cols = 512;
+  const uint32_t e_col = static_cast<uint32_t>(2 * p.block_t);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
+      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kEpiThreads);
+    }
+    ctrl->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_e);
+    tma_prefetch_desc(&tm_x);
+  }
+  if (warp == 1) {
+    tmem_alloc_1cta(smem_u32(&ctrl->tmem_base), tmem_cols);
+    tmem_relinquish_1cta();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      const int w0 = (tile % p.w_tiles) * kTileW;
+      const int t0 = (tile / p.w_tiles) * p.block_t;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full = smem_u32(&ctrl->full[stage]);
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          mbar_arrive_expect_tx(full, stage_bytes);
+          tma_load_2d(sa, &tm_w, full, kb * (kBlockK / 2), w0);
+          tma_load_2d(sa + kABytes, &tm_e, full, kb * (kBlockK / 8), w0);
+          tma_load_2d(sa + kABytes + kEBytes, &tm_x, full, kb * kBlockK, t0);
+        }
+        __syncwarp();
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    const uint32_t idesc = make_idesc_i8(kTileW, static_cast<uint32_t>(p.block_t), true);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
+                     kDevTimeoutTmemEmpty);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.block_t);
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, kDevTimeoutFull);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint64_t da = make_smem_desc(sa, 512, 64);
+          const uint64_t de = make_smem_desc(sa + kABytes, 128, 0);
+          const uint64_t db = make_smem_desc(sa + kABytes + kEBytes, 1024, 128);
+          tmem_cp_128x128b_1cta(tmem_base + e_col, de);
+          const int nk = (kb == p.num_kb - 1) ? p.last_ksteps : 2;
+          for (int k = 0; k < nk; ++k) {
+            // Per K=64 instruction: 32 compressed bytes of A (+2 address units), 64 bytes of
+            // B (+4) and two 32-bit metadata columns.
+            mma_sp_i8_1cta(d_tmem, da + 2 * k, db + 4 * k, tmem_base + e_col + 2 * k, idesc,
+                           (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
+        }
+        __syncwarp();
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+      if (ok && lane == 0) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
+      __syncwarp();
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;   // weight row within the tile
+    const int et = threadIdx.x - 64;
+    const bool geglu = p.epilogue == HY3D_EPI_GEGLU;
+    const int64_t ldo = geglu ? (p.N >> 1) : p.N;
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int w0 = (tile % p.w_tiles) * kTileW;
+      const int t0 = (tile / p.w_tiles) * p.block_t;
+      const int n = w0 + row_in_tile;
+      const bool n_ok = n < p.N;
+      float ws = 0.0f, bs = 0.0f;
+      if (p.out_dtype != HY3D_S32) {
+        for (int c = et; c < p.block_t; c += kEpiThreads)
+          ctrl->as[buf][c] = (t0 + c) < p.M ? p.act_scale[t0 + c] : 0.0f;
+        if (n_ok) {
+          ws = load_scalar(p.w_scale, p.ws_dtype, n);
+          bs = p.bias ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
+        }
+      }
+      epi_bar_sync();
+      if (ok) ok = mbar_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag,
+                             kDevTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) continue;
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(buf * p.block_t);
+      // GEGLU: weight rows come in blocks of 32 = 16 value rows then their 16 gate rows, so
+      // lanes 0-15 hold values and lanes 16-31 the matching gates.
+      const int64_t out_col = geglu ? ((w0 + quarter * 32) >> 1) + (lane & 15) : n;
+      for (int c = 0; c < p.block_t; c += 16) {
+        uint32_t r[16];
+        __syncwarp();
+        tmem_ld_x16(t_row + c, r);
+        tmem_ld_wait();
+        if (p.out_dtype == HY3D_S32) {
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t0 + c + j;
+              if (t < p.M)
+                reinterpret_cast<int32_t*>(p.out)[static_cast<int64_t>(t) * ldo + n] =
+                    static_cast<int32_t>(r[j]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + c + j;
+            float y = fmaf(static_cast<float>(static_cast<int32_t>(r[j])), ctrl->as[buf][c + j] * ws,
+                           bs);
+            if (p.epilogue == HY3D_EPI_GELU) y = gelu_erf(y);
+            if (geglu) {
+              const float g = __shfl_down_sync(0xffffffffu, y, 16);
+              y = y * gelu_erf(g);
+              if (lane < 16 && n_ok && t < p.M)
+                store_one(p.out, p.out_dtype, static_cast<int64_t>(t) * ldo + out_col, y);
+            } else if (n_ok && t < p.M) {
+              store_one(p.out, p.out_dtype, static_cast<int64_t>(t) * ldo + out_col, y);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) { }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_1cta(tmem_base, tmem_cols);
+  }
+}
+
+}  // namespace
+
+
+int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
+                  const uint32_t* w_meta, int64_t meta_ld, const void* w_scale, int ws_dtype,
+                  const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
+                  int64_t K, int epilogue, int block_t, cudaStream_t stream) {
+  if (!X || !w_comp || !w_meta || !out) return HY3D_ERR_ARG;
+  if (out_dtype != HY3D_F16 && out_dtype != HY3D_BF16 && out_dtype != HY3D_S32) return HY3D_ERR_ARG;
+  if (out_dtype != HY3D_S32 && (!act_scale || !w_scale)) return HY3D_ERR_ARG;
+  if (epilogue < HY3D_EPI_LINEAR || epilogue > HY3D_EPI_GEGLU) return HY3D_ERR_ARG;
+  if (out_dtype == HY3D_S32 && epilogue != HY3D_EPI_LINEAR) return HY3D_ERR_ARG;
+  if (ws_dtype < HY3D_F16 || ws_dtype > HY3D_F32) return HY3D_ERR_ARG;
+  if (bias && (bias_dtype < HY3D_F16 || bias_dtype > HY3D_F32)) return HY3D_ERR_ARG;
+  if (M < 0 || N <= 0 || K <= 0 || (K & 63) || (N & 15)) return HY3D_ERR_SHAPE;
+  if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return HY3D_ERR_SHAPE;
+  if (epilogue == HY3D_EPI_GEGLU && (N & 31)) return HY3D_ERR_SHAPE;
+  const int64_t kblocks = (K + kBlockK - 1) / kBlockK;
+  if (meta_ld != 4 * kblocks) return HY3D_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(w_comp) |
+       reinterpret_cast<uintptr_t>(w_meta) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return HY3D_ERR_SHAPE;
+  if (M == 0) return HY3D_OK;
+
+  if (block_t == 0) {
+    block_t = 192;
+    if (M < 192) block_t = static_cast<int>((M + 15) / 16 * 16);
+  }
+  if (block_t < 16 || block_t > kMaxBlockT || (block_t & 15)) return HY3D_ERR_SHAPE;
+
+  SparseArgs p;
+  p.act_scale = act_scale; p.w_scale = w_scale; p.bias = bias; p.out = out;
+  p.ws_dtype = ws_dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype; p.epilogue = epilogue;
+  p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
+  p.block_t = block_t;
+  p.w_tiles = static_cast<int>((N + kTileW - 1) / kTileW);
+  p.t_tiles = static_cast<int>((M + block_t - 1) / block_t);
+  p.num_kb = static_cast<int>(kblocks);
+  const int k_last = static_cast<int>(K - (kblocks - 1) * kBlockK);
+  p.last_ksteps = (k_last + 63) / 64;
+  const int stage_bytes = kABytes + kEBytes + block_t * 128;
+  const int fixed = static_cast<int>(sizeof(SparseCtrl)) + 1024;
+  int stages = (kSmemLimit - fixed) / stage_bytes;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 2) return HY3D_ERR_SHAPE;
+  p.stages = stages;
+  // One CTA per SM: the kernel allocates all 512 tensor-memory columns, so a second
+  // resident CTA would wait for them.  Keep the footprint above half an SM's shared memory.
+  int smem_bytes = stages * stage_bytes + fixed;
+  if (smem_bytes < 120 * 1024) smem_bytes = 120 * 1024;
+
+  CUtensorMap tm_w, tm_e, tm_x;
+  int rc = encode_tmap_2d_u8(&tm_w, w_comp, static_cast<uint64_t>(K / 2), static_cast<uint64_t>(N),
+                             static_cast<uint64_t>(K / 2), kBlockK / 2, kTileW, 64);
+  if (rc != HY3D_OK) return rc;
+  rc = encode_tmap_2d_u8(&tm_e, w_meta, static_cast<uint64_t>(meta_ld * 4), static_cast<uint64_t>(N),
+                         static_cast<uint64_t>(meta_ld * 4), kBlockK / 8, kTileW, 0);
+  if (rc != HY3D_OK) return rc;
+  rc = encode_tmap_2d_u8(&tm_x, X, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
+                         static_cast<uint64_t>(K), kBlockK, static_cast<uint32_t>(block_t), 128);
+  if (rc != HY3D_OK) return rc;
+
+  static bool attr_set[64] = {};
+  const int dev = current_device();
+  if (dev < 0 || dev >= 64) return HY3D_ERR_CUDA;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm_sparse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemLimit) != cudaSuccess)
+      return HY3D_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  const int sms = device_sm_count();
+  if (sms <= 0) return HY3D_ERR_CUDA;
+  const int total_tiles = p.w_tiles * p.t_tiles;
+  const int grid = total_tiles < sms ? total_tiles : sms;
+  gemm_sparse_kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_w, tm_e, tm_x, p);
+  return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
+}
+
+}  // namespace sparse
+
+using sparse::gemm_sparse24;
+
+}  // namespace hy3d

@@ -1,0 +1,217 @@
+// Per-token absmax activation quantiser and the stand-alone dequant+bias epilogue kernel.
+//
+// Quantiser arithmetic (bit-exact contract, checked against the CPU oracle):
+//     amax  = max_k |x[m,k]|                       (fp32)
+//     scale = max(amax, 1e-8f) / 127.0f            (IEEE division)
+//     q     = clamp(rint(x / scale), -128, 127)    (IEEE division, round-half-even)
+// The row is read ONCE with 16-byte loads and kept in registers between the absmax
+// reduction and the rounding pass, so the kernel moves 2*K + K + 4/M bytes per row.
+// The division is done as x * rcp(scale) with a guard: whenever the product lands within
+// 1e-4 of a rounding boundary (k + 0.5) the element is redone with a true IEEE division, so
+// the result always equals rint(x / scale).
+#include "common.cuh"
+
+namespace hy3d {
+namespace quant {
+namespace {
+
+constexpr int kQuantThreads = 256;
+
+template <bool kBf16>
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (kBf16) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    } else {
+      __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+      float2 t = __half22float2(h);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+}
+
+__device__ __forceinline__ int quant_one(float x, float scale, float inv) {
+  float t = x * inv;
+  float r = rintf(t);
+  // |t - r| close to 0.5 means the approximate quotient sits next to a rounding boundary;
+  // its error is below 3e-5 for |t| <= 128, so outside this band rint(t) == rint(x/scale).
+  if (fabsf(t - r) > 0.4999f) r = rintf(__fdiv_rn(x, scale));
+  r = fminf(fmaxf(r, -128.0f), 127.0f);
+  return static_cast<int>(r);
+}
+
+// G threads cooperate on one row (G a power of two, 1..256); each holds up to kMaxV
+// 16-byte vectors.  A block of 256 threads covers 256/G rows.
+template <bool kBf16, int kMaxV>
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_rows_kernel(const uint16_t* __restrict__ x, int64_t ldx, int8_t* __restrict__ q,
+                     float* __restrict__ scale_out, int64_t M, int K, int G) {
+  __shared__ float s_part[kQuantThreads / 32];
+  const int tid = threadIdx.x;
+  const int rows_per_block = kQuantThreads / G;
+  const int sub = tid % G;  // position within the row group
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_block + tid / G;
+  const bool row_ok = row < M;
+  const int nvec = K >> 3;
+
+  uint4 v[kMaxV];
+  float amax = 0.0f;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (row_ok ? row : 0) * ldx);
+#pragma unroll
+  for (int i = 0; i < kMaxV; ++i) {
+    const int c = sub + i * G;
+    if (row_ok && c < nvec) {
+      v[i] = __ldcs(src + c);
+    } else {
+      v[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kMaxV; ++i) {
+    float f[8];
+    unpack8<kBf16>(v[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+  }
+  // Reduce over the G threads of the row.
+  const int w = G < 32 ? G : 32;
+  for (int off = w >> 1; off > 0; off >>= 1)
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if (G > 32) {
+    const int warp = tid >> 5;
+    if ((tid & 31) == 0) s_part[warp] = amax;
+    __syncthreads();
+    const int warps_per_row = G >> 5;
+    const int first = (warp / warps_per_row) * warps_per_row;
+    amax = s_part[first];
+    for (int i = 1; i < warps_per_row; ++i) amax = fmaxf(amax, s_part[first + i]);
+  }
+  const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+  const float inv = __frcp_rn(scale);
+  if (row_ok && sub == 0) scale_out[row] = scale;
+
+  uint2* dst = reinterpret_cast<uint2*>(q + (row_ok ? row : 0) * static_cast<int64_t>(K));
+#pragma unroll
+  for (int i = 0; i < kMaxV; ++i) {
+    const int c = sub + i * G;
+    if (row_ok && c < nvec) {
+      float f[8];
+      unpack8<kBf16>(v[i], f);
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= (static_cast<uint32_t>(quant_one(f[j], scale, inv)) & 0xFFu) << (8 * j);
+        hi |= (static_cast<uint32_t>(quant_one(f[j + 4], scale, inv)) & 0xFFu) << (8 * j);
+      }
+      dst[c] = make_uint2(lo, hi);
+    }
+  }
+}
+
+template <bool kBf16>
+int launch_quantize(const void* x, int64_t M, int64_t K, int64_t ldx, int8_t* q, float* scale,
+                    cudaStream_t stream) {
+  const int nvec = static_cast<int>(K >> 3);
+  // Choose the power-of-two group size G and vectors-per-thread V (<= 8) that cover the row
+  // with the fewest idle vector slots; among equals prefer V near 4 (enough loads in flight
+  // per thread without starving the block of rows).
+  int G = 0, maxv = 0, best = 1 << 30;
+  for (int g = 1; g <= kQuantThreads; g <<= 1) {
+    const int v = (nvec + g - 1) / g;
+    if (v > 8) continue;
+    const int score = (g * v - nvec) * 1000 / nvec * 16 + (v > 4 ? v - 4 : 4 - v);
+    if (score < best) { best = score; G = g; maxv = v; }
+  }
+  if (G == 0) return HY3D_ERR_SHAPE;
+  const int rows_per_block = kQuantThreads / G;
+  const int64_t blocks = (M + rows_per_block - 1) / rows_per_block;
+  if (blocks > 0x7FFFFFFF) return HY3D_ERR_SHAPE;
+  const uint16_t* xp = reinterpret_cast<const uint16_t*>(x);
+  dim3 grid(static_cast<unsigned>(blocks));
+#define HY3D_LAUNCH_Q(V)                                                                   \
+  quantize_rows_kernel<kBf16, V><<<grid, kQuantThreads, 0, stream>>>(xp, ldx, q, scale, M, \
+                                                                     static_cast<int>(K), G)
+  switch (maxv) {
+    case 1: HY3D_LAUNCH_Q(1); break;
+    case 2: HY3D_LAUNCH_Q(2); break;
+    case 3: HY3D_LAUNCH_Q(3); break;
+    case 4: HY3D_LAUNCH_Q(4); break;
+    case 5: HY3D_LAUNCH_Q(5); break;
+    case 6: HY3D_LAUNCH_Q(6); break;
+    case 7: HY3D_LAUNCH_Q(7); break;
+    default: HY3D_LAUNCH_Q(8); break;
+  }
+#undef HY3D_LAUNCH_Q
+  return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
+}
+
+// out[m,n] = acc[m,n] * (act_scale[m] * w_scale[n]) + bias[n]; 8 columns per thread.
+__global__ void __launch_bounds__(256)
+dequant_bias_kernel(const int32_t* __restrict__ acc, const float* __restrict__ act_scale,
+                    const void* __restrict__ w_scale, int ws_dtype, const void* __restrict__ bias,
+                    int bias_dtype, void* __restrict__ out, int out_dtype, int64_t M, int64_t N) {
+  const int64_t nchunk = N >> 3;
+  const int64_t total = M * nchunk;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t m = i / nchunk;
+    const int64_t n0 = (i - m * nchunk) << 3;
+    const int4* src = reinterpret_cast<const int4*>(acc + m * N + n0);
+    const int4 a0 = src[0], a1 = src[1];
+    const int a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float as = act_scale[m];
+    float y[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = as * load_scalar(w_scale, ws_dtype, n0 + j);
+      const float b = bias ? load_scalar(bias, bias_dtype, n0 + j) : 0.0f;
+      y[j] = fmaf(static_cast<float>(a[j]), s, b);
+    }
+    uint4 o;
+    o.x = pack2(y[0], y[1], out_dtype);
+    o.y = pack2(y[2], y[3], out_dtype);
+    o.z = pack2(y[4], y[5], out_dtype);
+    o.w = pack2(y[6], y[7], out_dtype);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(out) + m * N + n0) = o;
+  }
+}
+
+}  // namespace
+
+int quantize_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* q,
+                  float* scale, cudaStream_t stream) {
+  if (!x || !q || !scale) return HY3D_ERR_ARG;
+  if (x_dtype != HY3D_F16 && x_dtype != HY3D_BF16) return HY3D_ERR_ARG;
+  if (M < 0 || K <= 0 || (K & 7) || K > 16384 || ldx < K || (ldx & 7)) return HY3D_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
+    return HY3D_ERR_SHAPE;
+  if (M == 0) return HY3D_OK;
+  return x_dtype == HY3D_BF16 ? launch_quantize<true>(x, M, K, ldx, q, scale, stream)
+                              : launch_quantize<false>(x, M, K, ldx, q, scale, stream);
+}
+
+int dequant_bias(const int32_t* acc, const float* act_scale, const void* w_scale, int ws_dtype,
+                 const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
+                 cudaStream_t stream) {
+  if (!acc || !act_scale || !w_scale || !out) return HY3D_ERR_ARG;
+  if (out_dtype != HY3D_F16 && out_dtype != HY3D_BF16) return HY3D_ERR_ARG;
+  if (M < 0 || N <= 0 || (N & 7)) return HY3D_ERR_SHAPE;
+  if (M == 0) return HY3D_OK;
+  const int64_t total = M * (N >> 3);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  dequant_bias_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      acc, act_scale, w_scale, ws_dtype, bias, bias_dtype, out, out_dtype, M, N);
+  return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
+}
+
+}  // namespace quant
+
+using quant::quantize_rows;
+using quant::dequant_bias;
+
+}  // namespace hy3d

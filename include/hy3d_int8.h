@@ -1,0 +1,172 @@
+/*
+ * hy3d_int8.h -- C ABI of the sm_100a W8A8 linear-layer library (libhy3d_int8.so).
+ *
+ * Every entry point takes raw device pointers, 64-bit sizes, small enums and a CUDA
+ * stream passed as `void*` (a cudaStream_t); it returns 0 on success or one of the
+ * HY3D_ERR_* codes below.  Nothing here allocates device memory: the caller owns all
+ * inputs, outputs and workspaces.  No C++ or torch type crosses this boundary.
+ *
+ * Each declaration cites the interface of WizardsForgeGames/Hunyuan3D-Tools that it
+ * stands in for (path within that project : lines).
+ */
+#ifndef HY3D_INT8_H_
+#define HY3D_INT8_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------ */
+#define HY3D_OK               0
+#define HY3D_ERR_ARG          1  /* null pointer, unknown enum value                      */
+#define HY3D_ERR_SHAPE        2  /* size / divisibility / alignment rule violated         */
+#define HY3D_ERR_CUDA         3  /* a CUDA runtime or driver call failed                  */
+#define HY3D_ERR_DEVICE       4  /* device is not compute capability 10.x                 */
+#define HY3D_ERR_TIMEOUT      5  /* a bounded device-side wait gave up (see last_status)  */
+#define HY3D_ERR_TOO_LARGE    6  /* size exceeds a fixed internal capacity                */
+
+/* ---- element types ------------------------------------------------------------------ */
+#define HY3D_F16   0
+#define HY3D_BF16  1
+#define HY3D_F32   2   /* scales / bias only                                              */
+#define HY3D_S32   3   /* GEMM output only: raw int32 accumulators, no rescale            */
+
+/* ---- GEMM epilogues ------------------------------------------------------------------ */
+#define HY3D_EPI_LINEAR  0  /* y = acc * (act_scale[m] * w_scale[n]) + bias[n]             */
+#define HY3D_EPI_GELU    1  /* y = gelu_erf(linear)                                        */
+#define HY3D_EPI_GEGLU   2  /* weights row-interleaved in blocks of 16 (value,gate):
+                               y[m, j] = value * gelu_erf(gate); output has N/2 columns   */
+
+/* Library version and build architecture ("sm_100a"). */
+int         hy3d_version(void);
+const char* hy3d_arch(void);
+const char* hy3d_status_string(int status);
+
+/* Reads (with a device synchronisation) and clears the device-side error word that a
+ * kernel sets when one of its bounded waits ran out.  0 = no error recorded. */
+int hy3d_last_device_status(int* status_out);
+
+/*
+ * Per-token (per-row) symmetric absmax quantisation: for each of the M rows
+ *     scale = max(max_k |x|, 1e-8) / 127 ;  q = clamp(rint(x / scale), -128, 127)
+ * x: (M,K) f16 or bf16, row pitch ldx elements.  q: (M,K) int8 contiguous.  scale: (M) f32.
+ * Requires K % 8 == 0, K <= 16384, 16-byte aligned x rows.
+ * Replaces: csrc/int8_gemm_tc.cu:190-242 (_tc_fused_quantize), csrc/int8_kernels.cu:26-88,
+ * 128-153 (fused_quantize_activation), csrc/int8_sparse_tc.cu:218-336, 1668-1707
+ * (sparse_quantize_act).
+ */
+int hy3d_quantize_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                       int8_t* q, float* scale, void* stream);
+
+/*
+ * Dense W8A8 GEMM with fused epilogue.
+ *   acc[m,n] = sum_k A[m,k] * B[n,k]          (int32, exact)
+ *   out      = epilogue(acc, act_scale, w_scale, bias)  in out_dtype (f16 / bf16), or the
+ *              raw accumulators when out_dtype == HY3D_S32 (scales and bias ignored).
+ * A: (M,K) int8 row-major.  B: (N,K) int8 row-major.  act_scale: (M) f32.
+ * w_scale: (N) of w_scale_dtype (f16/bf16/f32).  bias: (N) of bias_dtype, or NULL.
+ * out: (M, N) -- (M, N/2) for HY3D_EPI_GEGLU -- row-major, contiguous.
+ * Requires K % 16 == 0, N % 16 == 0 (N % 32 for GEGLU), 16-byte aligned pointers.
+ * cta_group: 0 = choose, 1 = one CTA per tile, 2 = CTA pair (256-row tiles).
+ * block_n:   0 = choose, else the tile width (multiple of 16, <= 256).
+ * Replaces: csrc/int8_gemm_tc.cu:36-184, 254-309 (int8_gemm_tc) and the epilogue-only
+ * kernel csrc/int8_kernels.cu:99-121 (fused_dequantize_bias) that followed torch::_int_mm.
+ */
+int hy3d_gemm_w8a8_dense(const int8_t* A, const int8_t* B, const float* act_scale,
+                         const void* w_scale, int w_scale_dtype,
+                         const void* bias, int bias_dtype,
+                         void* out, int out_dtype,
+                         int64_t M, int64_t N, int64_t K,
+                         int epilogue, int cta_group, int block_n, void* stream);
+
+/*
+ * Whole dense linear layer: quantise x per token into the caller's workspace, then the
+ * GEMM above.  x: (M,K) f16/bf16; q_ws: (M,K) int8 workspace; scale_ws: (M) f32 workspace.
+ * Replaces: csrc/int8_gemm_tc.cu:312-320 (int8_linear_tc), csrc/int8_kernels.cu:193-210
+ * (int8_linear_fused).
+ */
+int hy3d_linear_w8a8_dense(const void* x, int x_dtype, int64_t ldx,
+                           int8_t* q_ws, float* scale_ws,
+                           const int8_t* B, const void* w_scale, int w_scale_dtype,
+                           const void* bias, int bias_dtype,
+                           void* out, int out_dtype,
+                           int64_t M, int64_t N, int64_t K,
+                           int epilogue, int cta_group, int block_n, void* stream);
+
+/*
+ * Offline 2:4 prune + compress + metadata pack of an int8 weight matrix, one pass.
+ * Per group of 4 along K the two smallest |w| are dropped; the tie rule is
+ *   min1=0,min2=1; if |w0|>|w1| swap; for i in 2,3: if |wi|<|w[min1]| {min2=min1;min1=i}
+ *   else if |wi|<|w[min2]| {min2=i}      (both comparisons strict)
+ * and the survivors keep ascending index order (idx0 < idx1).
+ * w: (N,K) int8.  comp: (N,K/2) int8.  meta_raw (optional, may be NULL): (N*K/4) bytes,
+ * one nibble idx0 | idx1<<2 per group.  meta_packed (optional): (N, meta_ld) uint32 words,
+ * word c of a row = the 8 nibbles of K chunk [32c, 32c+32), least-significant first;
+ * meta_ld >= K/32, words [K/32, meta_ld) of each row are written as 0x44444444.
+ * Requires K % 32 == 0 (K % 16 when meta_packed is NULL), 16-byte aligned w rows.
+ * Replaces: csrc/int8_sparse_tc.cu:152-212 (prune_compress_kernel), 416-437
+ * (pack_metadata_kernel), 1558-1585 (sparse_prune_compress), 1616-1665
+ * (sparse_prune_and_pack).
+ */
+int hy3d_prune_pack_24(const int8_t* w, int64_t N, int64_t K,
+                       int8_t* comp, uint8_t* meta_raw,
+                       uint32_t* meta_packed, int64_t meta_ld, void* stream);
+
+/*
+ * 2:4 structured-sparse W8A8 GEMM with the same epilogues as the dense one.
+ *   acc[m,n] = sum_k X[m,k] * Wpruned[n,k]
+ * X: (M,K) int8.  w_comp: (N,K/2) int8.  w_meta: (N, meta_ld) uint32 as written by
+ * hy3d_prune_pack_24 with meta_ld = 4*ceil(K/128).  Other arguments as for the dense GEMM.
+ * Requires K % 64 == 0, N % 16 == 0.  block_m: 0 = choose, else the token-tile width
+ * (multiple of 16, <= 256).
+ * Replaces: csrc/int8_sparse_tc.cu:535-1123, 1758-1929 (sparse_int8_gemm) and 519-531
+ * (splitk_reduce_kernel; there is no split-K here, accumulation stays int32).
+ */
+int hy3d_gemm_w8a8_sparse24(const int8_t* X, const float* act_scale,
+                            const int8_t* w_comp, const uint32_t* w_meta, int64_t meta_ld,
+                            const void* w_scale, int w_scale_dtype,
+                            const void* bias, int bias_dtype,
+                            void* out, int out_dtype,
+                            int64_t M, int64_t N, int64_t K,
+                            int epilogue, int block_m, void* stream);
+
+/*
+ * Whole sparse linear layer: quantise + sparse GEMM.
+ * Replaces: csrc/int8_sparse_tc.cu:2006-2044 (sparse_int8_linear, sparse_int8_linear_ex).
+ */
+int hy3d_linear_w8a8_sparse24(const void* x, int x_dtype, int64_t ldx,
+                              int8_t* q_ws, float* scale_ws,
+                              const int8_t* w_comp, const uint32_t* w_meta, int64_t meta_ld,
+                              const void* w_scale, int w_scale_dtype,
+                              const void* bias, int bias_dtype,
+                              void* out, int out_dtype,
+                              int64_t M, int64_t N, int64_t K,
+                              int epilogue, int block_m, void* stream);
+
+/*
+ * Epilogue-only kernel on an int32 accumulator matrix:
+ *   out[m,n] = acc[m,n] * (act_scale[m] * w_scale[n]) + bias[n]
+ * Replaces: csrc/int8_kernels.cu:99-121, 156-190 (fused_dequantize_bias).
+ */
+int hy3d_dequant_bias(const int32_t* acc, const float* act_scale,
+                      const void* w_scale, int w_scale_dtype,
+                      const void* bias, int bias_dtype,
+                      void* out, int out_dtype, int64_t M, int64_t N, void* stream);
+
+/*
+ * Known-answer hook: ONE tensor-core tile product on a single CTA.
+ *   sparse == 0: D(128 x n) = A(128 x k) * B(n x k)^T, k = 32 * ksteps  (tcgen05.mma kind::i8)
+ *   sparse == 1: A is 2:4 compressed (128 x k/2) with meta (128 x 4*ceil(k/128)) words,
+ *                k = 64 * ksteps                                 (tcgen05.mma.sp kind::i8)
+ * n: multiple of 16 in [16,256]; ksteps in [1,4] (dense) or [1,2] (sparse).  d: (128,n) int32.
+ * Replaces: csrc/int8_sparse_tc.cu:350-408, 1587-1614 (test_mma_sp).
+ */
+int hy3d_mma_kat(const int8_t* a, const int8_t* b, const uint32_t* meta,
+                 int32_t* d, int n, int ksteps, int sparse, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HY3D_INT8_H_ */
