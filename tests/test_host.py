@@ -1,0 +1,139 @@
+"""CPU: the C-ABI library loads and exports what the header declares; the host-side mirror of
+the reference's module behaves like it where no GPU is needed, and fails loudly where one is."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+import torch.nn as nn
+
+from conftest import ROOT, as_half
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "hy3d_int8.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hy3d_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(build_mod):
+    lib = build_mod.load_library()
+    names = _declared_symbols()
+    assert len(names) >= 12
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in hy3d_int8.h but not exported"
+
+
+def test_binding_table_covers_header(build_mod):
+    binding = __import__("importlib").import_module("hunyuan3d-tools_b200.csrc._binding")
+    declared = set(_declared_symbols())
+    bound = set(binding.SIGNATURES) | {"hy3d_arch", "hy3d_status_string"}
+    assert declared == bound
+
+
+def test_library_identity(build_mod):
+    binding = __import__("importlib").import_module("hunyuan3d-tools_b200.csrc._binding")
+    lib = binding.configure(build_mod.load_library())
+    assert lib.hy3d_arch() == b"sm_100a"
+    assert lib.hy3d_version() >= 100
+    assert b"alignment" in lib.hy3d_status_string(2)
+
+
+def test_build_flags_are_sm100a_only(build_mod):
+    flags = " ".join(build_mod.cuda_flags())
+    assert "arch=compute_100a,code=sm_100a" in flags
+    assert "use_fast_math" not in flags
+    assert flags.count("-gencode") == 1
+
+
+def test_loader_names_match_reference(build_mod):
+    for name in ("load_int8_kernels", "load_tc_gemm", "load_sparse_tc"):
+        assert callable(getattr(build_mod, name))
+    tc = build_mod.load_tc_gemm()
+    sp = build_mod.load_sparse_tc()
+    ik = build_mod.load_int8_kernels()
+    for fn in ("int8_linear_tc", "int8_gemm_tc"):
+        assert callable(getattr(tc, fn))
+    for fn in ("sparse_prune_compress", "sparse_prune_and_pack", "sparse_quantize_act",
+               "sparse_int8_gemm", "sparse_int8_linear", "sparse_int8_linear_ex",
+               "sparse_int8_linear_path", "test_mma_sp"):
+        assert callable(getattr(sp, fn))
+    for fn in ("fused_quantize_activation", "fused_dequantize_bias", "int8_linear_fused"):
+        assert callable(getattr(ik, fn))
+
+
+def test_from_linear_matches_reference_buffers(qu, golden):
+    lin = nn.Linear(320, 128).half()
+    lin.weight.data = as_half(golden["a_weight"])
+    lin.bias.data = as_half(golden["a_bias"])
+    layer = qu.Int8Linear.from_linear(lin)
+    assert torch.equal(layer.weight_int8_nk, torch.from_numpy(golden["a_weight_int8_nk"]))
+    assert torch.equal(layer.weight_scale, as_half(golden["a_weight_scale"]))
+    assert torch.equal(layer.bias, as_half(golden["a_layer_bias"]))
+    assert layer.weight_int8_nk.shape == (128, 320) and layer.weight_int8_nk.dtype == torch.int8
+    assert layer.mode == "tc" and layer._tc_ok and layer._sparse_ok
+    assert set(dict(layer.named_buffers())) == {"weight_int8_nk", "weight_scale", "bias"}
+
+
+def test_bf16_source_keeps_bf16_scales(qu):
+    lin = nn.Linear(128, 128, bias=False).bfloat16()
+    layer = qu.Int8Linear.from_linear(lin)
+    assert layer.weight_scale.dtype == torch.bfloat16 and layer.bias is None
+
+
+def test_model_surgery_stats_match_reference(qu, golden):
+    torch.manual_seed(4)
+    toy = nn.Sequential(nn.Linear(256, 512), nn.GELU(), nn.Linear(512, 64), nn.Linear(64, 256),
+                        nn.Sequential(nn.Linear(256, 256)))
+    stats = qu.quantize_model_tensorcore(toy, min_features=128, verbose=False)
+    got = [stats["total_params"], stats["quantized_params"], stats["skipped_params"],
+           stats["num_replaced"], stats.get("tc_eligible", 0)]
+    assert got == golden["toy_stats"].tolist()
+    assert isinstance(toy[0], qu.Int8Linear) and isinstance(toy[2], nn.Linear)
+    assert isinstance(toy[4][0], qu.Int8Linear)
+
+
+def test_ineligible_shapes_stay_linear(qu):
+    m = nn.Sequential(nn.Linear(200, 256), nn.Linear(256, 136))
+    stats = qu.quantize_model_tensorcore(m, verbose=False)
+    assert isinstance(m[0], nn.Linear) and isinstance(m[1], nn.Linear)
+    assert stats["num_replaced"] == 0 and stats["kept_fp16"] == 2
+
+
+def test_forward_on_cpu_fails_loudly(qu):
+    layer = qu.Int8Linear.from_linear(nn.Linear(128, 128).half())
+    with pytest.raises(RuntimeError, match="CUDA"):
+        layer(torch.randn(4, 128).half())
+
+
+def test_sparse_conversion_on_cpu_fails_loudly(qu):
+    with pytest.raises(RuntimeError, match="CUDA"):
+        qu.Int8Linear.from_linear_sparse(nn.Linear(640, 128).half())
+
+
+def test_state_dict_roundtrip_dense(qu):
+    a = qu.Int8Linear.from_linear(nn.Linear(128, 256).half())
+    b = qu.Int8Linear(128, 256, bias=True)
+    b.load_state_dict(a.state_dict())
+    assert torch.equal(a.weight_int8_nk, b.weight_int8_nk) and torch.equal(a.weight_scale, b.weight_scale)
+
+
+def test_geglu_row_interleave(qu):
+    lin = nn.Linear(128, 64).half()
+    layer = qu.Int8Linear.from_linear(lin)
+    before = layer.weight_int8_nk.clone()
+    layer.interleave_geglu_rows()
+    assert layer.epilogue == "geglu"
+    assert torch.equal(layer.weight_int8_nk[:16], before[:16])
+    assert torch.equal(layer.weight_int8_nk[16:32], before[32:48])
+    assert torch.equal(layer.weight_int8_nk[32:48], before[16:32])
+
+
+def test_oracle_is_not_imported_by_the_product():
+    pkg_dir = os.path.join(ROOT, "hunyuan3d-tools_b200")
+    for dirpath, _, files in os.walk(pkg_dir):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "import oracle" not in text and "from oracle" not in text, f
