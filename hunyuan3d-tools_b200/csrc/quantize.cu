@@ -184,9 +184,10 @@ dequant_bias_kernel(const int32_t* __restrict__ acc, const float* __restrict__ a
 
 int quantize_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* q,
                   float* scale, cudaStream_t stream) {
-  if (!x || !q || !scale) return HY3D_ERR_ARG;
   if (x_dtype != HY3D_F16 && x_dtype != HY3D_BF16) return HY3D_ERR_ARG;
   if (M < 0 || K <= 0 || (K & 7) || K > 16384 || ldx < K || (ldx & 7)) return HY3D_ERR_SHAPE;
+  if (M == 0) return HY3D_OK;
+  if (!x || !q || !scale) return HY3D_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
     return HY3D_ERR_SHAPE;
   if (M == 0) return HY3D_OK;
