@@ -3,12 +3,15 @@
 // One persistent CTA per SM walks 128 x block_n output tiles.  Roles by warp:
 //   warp 0      TMA producer: A (128 x 128 B) and B (block_n x 128 B) boxes, 128-byte swizzle,
 //               into a ring of shared-memory stages, signalled through "full" mbarriers.
-//   warp 1      owns tensor memory; one elected thread issues tcgen05.mma kind::i8
+//   warp 1      owns tensor memory; one thread issues tcgen05.mma kind::i8
 //               (128 x block_n x 32 per instruction, int32 accumulators in tensor memory) and
 //               commits each stage back to its "empty" mbarrier.
-//   warps 2-5   epilogue: tcgen05.ld the accumulators (one output row per thread),
-//               acc * (act_scale[m] * w_scale[n]) + bias[n], optional GELU / GEGLU, pack to
-//               bf16 / fp16 (or raw int32) and store.
+//   warps 2-9   epilogue, two warps per 32-lane quarter of tensor memory, alternating over
+//               32-column slabs: tcgen05.ld, acc * (act_scale[m] * w_scale[n]) + bias[n],
+//               optional GELU / GEGLU, pack to bf16 / fp16 into a 64-byte-swizzled staging
+//               buffer, one TMA store per slab (rows and columns outside the matrix are
+//               clipped by the tensor map).  Raw int32 output and tile widths that are not a
+//               multiple of the slab use plain 16-byte stores instead.
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the MMAs of
 // tile i+1.  Every wait is bounded; a wait that runs out records a code in the device
 // status word and all roles fall through to the common teardown.
@@ -27,8 +30,11 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kBlockKBytes = 128;   // one 128-byte swizzle row of int8 = 128 K elements
 constexpr int kMaxStages = 8;
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;
+constexpr int kSlabCols = 32;                       // output columns per TMA store
+constexpr int kSlabBytes = 32 * kSlabCols * 2;      // 32 rows x 64 B
 constexpr int kSmemLimit = 227 * 1024;
 
 struct DenseArgs {
@@ -38,28 +44,34 @@ struct DenseArgs {
   void* out;
   int ws_dtype, bias_dtype, out_dtype, epilogue;
   int M, N, K;
-  int block_n, stages, acc_cols;
+  int block_n, stages, acc_cols, tma_store;
   int m_tiles, n_tiles, num_kb, last_ksteps;
 };
 
-struct __align__(8) DenseCtrl {
+struct __align__(16) DenseCtrl {
+  float ws[2][256];     // per-column weight scales of the current tile, per accumulator buffer
+  float bs[2][256];     // per-column bias
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  float ws[2][256];
-  float bs[2][256];
 };
 
 __device__ __forceinline__ void epi_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
 }
 
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                  const DenseArgs p) {
+                  const __grid_constant__ CUtensorMap tm_o, const DenseArgs p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -69,7 +81,9 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const uint32_t a_bytes = kTileM * kBlockKBytes;
   const uint32_t b_bytes = static_cast<uint32_t>(p.block_n) * kBlockKBytes;
   const uint32_t stage_bytes = a_bytes + b_bytes;
-  DenseCtrl* ctrl = reinterpret_cast<DenseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
+  DenseCtrl* ctrl = reinterpret_cast<DenseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes +
+                                                 kEpiWarps * kSlabBytes);
   volatile int* abort_flag = &ctrl->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -89,6 +103,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     fence_barrier_init();
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
+    if (p.tma_store) tma_prefetch_desc(&tm_o);
   }
   if (warp == 1) {
     tmem_alloc_1cta(smem_u32(&ctrl->tmem_base), static_cast<uint32_t>(2 * p.acc_cols));
@@ -164,10 +179,14 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   } else {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;            // tensor-memory lane quarter this warp may read
+    const int half = (warp - 2) >> 2;        // which of the two warps sharing that quarter
     const int row_in_tile = quarter * 32 + lane;
-    const int et = threadIdx.x - 64;         // 0..127
+    const int et = threadIdx.x - 64;         // 0..255
     const bool geglu = p.epilogue == HY3D_EPI_GEGLU;
+    const bool gelu = p.epilogue == HY3D_EPI_GELU;
     const int64_t ldo = geglu ? (p.N >> 1) : p.N;
+    const uint32_t stage_buf = staging_base + static_cast<uint32_t>(warp - 2) * kSlabBytes;
+    const int acc_per_slab = geglu ? 2 * kSlabCols : kSlabCols;
     bool ok = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
@@ -193,8 +212,76 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const float as = (row_ok && p.out_dtype != HY3D_S32) ? p.act_scale[m] : 0.0f;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(buf * p.acc_cols);
-      if (!geglu) {
-        for (int c = 0; c < p.block_n; c += 16) {
+      const float* wsb = ctrl->ws[buf];
+      const float* bsb = ctrl->bs[buf];
+      if (p.tma_store) {
+        const int nslab = p.block_n / acc_per_slab;
+        for (int s = half; s < nslab; s += 2) {
+          const int c0 = s * acc_per_slab;
+          uint32_t packed[16];
+          __syncwarp();
+          if (!geglu) {
+            uint32_t r[32];
+            tmem_ld_x32(t_row + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 w4 = *reinterpret_cast<const float4*>(wsb + c0 + 4 * q);
+              const float4 b4 = *reinterpret_cast<const float4*>(bsb + c0 + 4 * q);
+              float y0 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])), as * w4.x, b4.x);
+              float y1 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 1])), as * w4.y, b4.y);
+              float y2 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])), as * w4.z, b4.z);
+              float y3 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 3])), as * w4.w, b4.w);
+              if (gelu) { y0 = gelu_erf(y0); y1 = gelu_erf(y1); y2 = gelu_erf(y2); y3 = gelu_erf(y3); }
+              packed[2 * q] = pack2(y0, y1, p.out_dtype);
+              packed[2 * q + 1] = pack2(y2, y3, p.out_dtype);
+            }
+          } else {
+            // 64 accumulator columns = two blocks of (16 value | 16 gate) -> 32 outputs.
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+              uint32_t rv[16], rg[16];
+              const int cb = c0 + 32 * b;
+              tmem_ld_x16(t_row + cb, rv);
+              tmem_ld_x16(t_row + cb + 16, rg);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; j += 2) {
+                float y[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                  const float v = fmaf(static_cast<float>(static_cast<int32_t>(rv[j + u])),
+                                       as * wsb[cb + j + u], bsb[cb + j + u]);
+                  const float g = fmaf(static_cast<float>(static_cast<int32_t>(rg[j + u])),
+                                       as * wsb[cb + 16 + j + u], bsb[cb + 16 + j + u]);
+                  y[u] = v * gelu_erf(g);
+                }
+                packed[8 * b + (j >> 1)] = pack2(y[0], y[1], p.out_dtype);
+              }
+            }
+          }
+          // The previous TMA store of this warp must have finished reading the staging
+          // buffer before it is overwritten (bulk groups are tracked per issuing thread).
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+          // 32 rows x 64 B, 64-byte swizzle: 16-byte chunk c of row r sits at c ^ ((r >> 1) & 3).
+          const uint32_t row_addr = stage_buf + static_cast<uint32_t>(lane) * 64u;
+          const uint32_t sw = (static_cast<uint32_t>(lane) >> 1) & 3u;
+#pragma unroll
+          for (uint32_t c = 0; c < 4; ++c)
+            st_shared_v4(row_addr + ((c ^ sw) << 4), packed[4 * c], packed[4 * c + 1],
+                         packed[4 * c + 2], packed[4 * c + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int out_col = geglu ? ((n0 + c0) >> 1) : (n0 + c0);
+            const int out_row = m0 + quarter * 32;
+            if (out_col < ldo && out_row < p.M) tma_store_2d(&tm_o, stage_buf, out_col * 2, out_row);
+            tma_store_commit();
+          }
+        }
+      } else if (!geglu) {
+        for (int c = 16 * half; c < p.block_n; c += 32) {
           uint32_t r[16];
           __syncwarp();
           tmem_ld_x16(t_row + c, r);
@@ -212,9 +299,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             float y[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              y[j] = fmaf(static_cast<float>(static_cast<int32_t>(r[j])), as * ctrl->ws[buf][c + j],
-                          ctrl->bs[buf][c + j]);
-              if (p.epilogue == HY3D_EPI_GELU) y[j] = gelu_erf(y[j]);
+              y[j] = fmaf(static_cast<float>(static_cast<int32_t>(r[j])), as * wsb[c + j], bsb[c + j]);
+              if (gelu) y[j] = gelu_erf(y[j]);
             }
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) +
                                                   static_cast<int64_t>(m) * ldo + n);
@@ -226,7 +312,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
       } else {
         // Columns come in blocks of 32: 16 "value" columns then their 16 "gate" columns.
-        for (int c = 0; c < p.block_n; c += 32) {
+        for (int c = 32 * half; c < p.block_n; c += 64) {
           uint32_t rv[16], rg[16];
           __syncwarp();
           tmem_ld_x16(t_row + c, rv);
@@ -237,10 +323,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             float y[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const float v = fmaf(static_cast<float>(static_cast<int32_t>(rv[j])),
-                                   as * ctrl->ws[buf][c + j], ctrl->bs[buf][c + j]);
+              const float v = fmaf(static_cast<float>(static_cast<int32_t>(rv[j])), as * wsb[c + j],
+                                   bsb[c + j]);
               const float g = fmaf(static_cast<float>(static_cast<int32_t>(rg[j])),
-                                   as * ctrl->ws[buf][c + 16 + j], ctrl->bs[buf][c + 16 + j]);
+                                   as * wsb[c + 16 + j], bsb[c + 16 + j]);
               y[j] = v * gelu_erf(g);
             }
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) +
@@ -256,6 +342,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
     }
+    // Global writes of the bulk stores must be complete before the CTA retires.
+    if (p.tma_store && lane == 0) tma_store_wait_all<0>();
   }
 
   // ---------------- teardown ----------------
@@ -275,14 +363,11 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 
 }  // namespace
 
-
 int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale,
                int ws_dtype, const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M,
                int64_t N, int64_t K, int epilogue, int cta_group, int block_n,
                cudaStream_t stream) {
-  if (!A || !B || !out) return HY3D_ERR_ARG;
   if (out_dtype != HY3D_F16 && out_dtype != HY3D_BF16 && out_dtype != HY3D_S32) return HY3D_ERR_ARG;
-  if (out_dtype != HY3D_S32 && (!act_scale || !w_scale)) return HY3D_ERR_ARG;
   if (epilogue < HY3D_EPI_LINEAR || epilogue > HY3D_EPI_GEGLU) return HY3D_ERR_ARG;
   if (out_dtype == HY3D_S32 && epilogue != HY3D_EPI_LINEAR) return HY3D_ERR_ARG;
   if (ws_dtype < HY3D_F16 || ws_dtype > HY3D_F32) return HY3D_ERR_ARG;
@@ -292,18 +377,20 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return HY3D_ERR_SHAPE;
   const bool geglu = epilogue == HY3D_EPI_GEGLU;
   if (geglu && (N & 31)) return HY3D_ERR_SHAPE;
+  if (M == 0) return HY3D_OK;
+  if (!A || !B || !out) return HY3D_ERR_ARG;
+  if (out_dtype != HY3D_S32 && (!act_scale || !w_scale)) return HY3D_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
        reinterpret_cast<uintptr_t>(out)) & 15)
     return HY3D_ERR_SHAPE;
-  if (M == 0) return HY3D_OK;
 
   if (block_n == 0) {
-    // Widest tile that divides N evenly; otherwise the widest one (ragged last tile).
+    // Widest tile (multiple of 32 so the TMA-store epilogue applies) that divides N evenly;
+    // otherwise the widest one with a ragged last tile.
     block_n = N >= 256 ? 256 : static_cast<int>(N);
-    for (int bn = 256; bn >= 128; bn -= 16) {
-      if (N % bn == 0) { block_n = bn; break; }
+    for (int bn = 256; bn >= 128; bn -= 32) {
+      if (N >= bn && N % bn == 0) { block_n = bn; break; }
     }
-    if (N < 256) block_n = static_cast<int>(N);
   }
   if (block_n < 16 || block_n > 256 || (block_n & 15) || (geglu && (block_n & 31)))
     return HY3D_ERR_SHAPE;
@@ -321,21 +408,30 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   p.num_kb = static_cast<int>((K + kBlockKBytes - 1) / kBlockKBytes);
   const int k_last = static_cast<int>(K - static_cast<int64_t>(p.num_kb - 1) * kBlockKBytes);
   p.last_ksteps = (k_last + 31) / 32;
+  p.tma_store = (out_dtype != HY3D_S32 && block_n % (geglu ? 2 * kSlabCols : kSlabCols) == 0) ? 1 : 0;
   const int stage_bytes = kTileM * kBlockKBytes + block_n * kBlockKBytes;
-  const int fixed = static_cast<int>(sizeof(DenseCtrl)) + 1024;
+  const int fixed = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * kSlabBytes + 1024;
   int stages = (kSmemLimit - fixed) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return HY3D_ERR_SHAPE;
   p.stages = stages;
   const int smem_bytes = stages * stage_bytes + fixed;
 
-  CUtensorMap tm_a, tm_b;
+  CUtensorMap tm_a, tm_b, tm_o;
   int rc = encode_tmap_2d_u8(&tm_a, A, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
                              static_cast<uint64_t>(K), kBlockKBytes, kTileM, 128);
   if (rc != HY3D_OK) return rc;
   rc = encode_tmap_2d_u8(&tm_b, B, static_cast<uint64_t>(K), static_cast<uint64_t>(N),
                          static_cast<uint64_t>(K), kBlockKBytes, static_cast<uint32_t>(block_n), 128);
   if (rc != HY3D_OK) return rc;
+  if (p.tma_store) {
+    const uint64_t row_bytes = static_cast<uint64_t>(geglu ? N / 2 : N) * 2;
+    rc = encode_tmap_2d_u8(&tm_o, out, row_bytes, static_cast<uint64_t>(M), row_bytes,
+                           kSlabCols * 2, 32, 64);
+    if (rc != HY3D_OK) return rc;
+  } else {
+    tm_o = tm_a;   // unused by the kernel
+  }
 
   static bool attr_set[64] = {};
   const int dev = current_device();
@@ -350,7 +446,7 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.m_tiles * p.n_tiles;
   const int grid = total_tiles < sms ? total_tiles : sms;
-  gemm_dense_kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_a, tm_b, p);
+  gemm_dense_kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_a, tm_b, tm_o, p);
   return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
 }
 
