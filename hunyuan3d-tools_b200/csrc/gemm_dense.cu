@@ -16,6 +16,7 @@
 // tile i+1.  Every wait is bounded; a wait that runs out records a code in the device
 // status word and all roles fall through to the common teardown.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace hy3d {
 // Host-side helpers implemented in capi.cu.
@@ -44,13 +45,13 @@ struct DenseArgs {
   void* out;
   int ws_dtype, bias_dtype, out_dtype, epilogue;
   int M, N, K;
-  int block_n, stages, acc_cols, tma_store;
+  int block_n, stages, acc_cols, tma_store, store_bufs;
   int m_tiles, n_tiles, num_kb, last_ksteps;
 };
 
 struct __align__(16) DenseCtrl {
-  float ws[2][256];     // per-column weight scales of the current tile, per accumulator buffer
-  float bs[2][256];     // per-column bias
+  float ws[256];        // per-column weight scales of the current tile columns
+  float bs[256];        // per-column bias
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
@@ -69,6 +70,82 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
                : "memory");
 }
 
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2t(float a, float b) {
+  if (kBf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// 32 accumulator columns of one row -> 32 outputs packed in 16 words.
+template <bool kBf16, int kEpi>
+__device__ __forceinline__ void slab_math(const uint32_t (&r)[32], float as, const float* wsb,
+                                          const float* bsb, uint32_t (&packed)[16]) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float4 w4 = *reinterpret_cast<const float4*>(wsb + 4 * q);
+    const float4 b4 = *reinterpret_cast<const float4*>(bsb + 4 * q);
+    float y0 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])), as * w4.x, b4.x);
+    float y1 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 1])), as * w4.y, b4.y);
+    float y2 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])), as * w4.z, b4.z);
+    float y3 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 3])), as * w4.w, b4.w);
+    if (kEpi == HY3D_EPI_GELU) {
+      y0 = gelu_erf(y0); y1 = gelu_erf(y1); y2 = gelu_erf(y2); y3 = gelu_erf(y3);
+    }
+    packed[2 * q] = pack2t<kBf16>(y0, y1);
+    packed[2 * q + 1] = pack2t<kBf16>(y2, y3);
+  }
+}
+
+// 64 accumulator columns = two blocks of (16 value | 16 gate) -> 32 outputs in 16 words.
+template <bool kBf16>
+__device__ __forceinline__ void slab_math_geglu(const uint32_t (&rv)[16], const uint32_t (&rg)[16],
+                                                float as, const float* wsb, const float* bsb,
+                                                uint32_t* packed8) {
+#pragma unroll
+  for (int j = 0; j < 16; j += 2) {
+    float y[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const float v = fmaf(static_cast<float>(static_cast<int32_t>(rv[j + u])), as * wsb[j + u],
+                           bsb[j + u]);
+      const float g = fmaf(static_cast<float>(static_cast<int32_t>(rg[j + u])),
+                           as * wsb[16 + j + u], bsb[16 + j + u]);
+      y[u] = v * gelu_erf(g);
+    }
+    packed8[j >> 1] = pack2t<kBf16>(y[0], y[1]);
+  }
+}
+
+// Writes one packed 32 x 32 slab row into the warp's staging buffer (64-byte swizzle: 16-byte
+// chunk c of row r sits at c ^ ((r >> 1) & 3)) and lets lane 0 issue the TMA store.
+// `pending_ok` = number of earlier bulk groups of this warp that may still be reading
+// shared memory (1 with two staging buffers, 0 with one).
+__device__ __forceinline__ void slab_store(const uint32_t (&packed)[16], uint32_t buf_addr, int lane,
+                                           int pending_ok, const CUtensorMap* tm_o, int x_bytes,
+                                           int y_row, bool in_range) {
+  if (lane == 0) {
+    if (pending_ok) tma_store_wait_read<1>(); else tma_store_wait_read<0>();
+  }
+  __syncwarp();
+  const uint32_t row_addr = buf_addr + static_cast<uint32_t>(lane) * 64u;
+  const uint32_t sw = (static_cast<uint32_t>(lane) >> 1) & 3u;
+#pragma unroll
+  for (uint32_t c = 0; c < 4; ++c)
+    st_shared_v4(row_addr + ((c ^ sw) << 4), packed[4 * c], packed[4 * c + 1], packed[4 * c + 2],
+                 packed[4 * c + 3]);
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    if (in_range) tma_store_2d(tm_o, buf_addr, x_bytes, y_row);
+    tma_store_commit();
+  }
+}
+
+template <bool kBf16, int kEpi>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_o, const DenseArgs p) {
@@ -83,7 +160,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const uint32_t stage_bytes = a_bytes + b_bytes;
   const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
   DenseCtrl* ctrl = reinterpret_cast<DenseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes +
-                                                 kEpiWarps * kSlabBytes);
+                                                 kEpiWarps * p.store_bufs * kSlabBytes);
   volatile int* abort_flag = &ctrl->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -182,62 +259,113 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int half = (warp - 2) >> 2;        // which of the two warps sharing that quarter
     const int row_in_tile = quarter * 32 + lane;
     const int et = threadIdx.x - 64;         // 0..255
-    const bool geglu = p.epilogue == HY3D_EPI_GEGLU;
-    const bool gelu = p.epilogue == HY3D_EPI_GELU;
+    const bool geglu = kEpi == HY3D_EPI_GEGLU;
+    const bool gelu = kEpi == HY3D_EPI_GELU;
     const int64_t ldo = geglu ? (p.N >> 1) : p.N;
-    const uint32_t stage_buf = staging_base + static_cast<uint32_t>(warp - 2) * kSlabBytes;
+    const uint32_t stage_buf = staging_base + static_cast<uint32_t>((warp - 2) * p.store_bufs) * kSlabBytes;
     const int acc_per_slab = geglu ? 2 * kSlabCols : kSlabCols;
     bool ok = true;
     int it = 0;
+    int cur_n0 = -1;
+    const bool scaled = p.out_dtype != HY3D_S32;
+    // The activation scale of the NEXT tile's row is fetched one tile ahead, and the
+    // per-column scales / bias are refilled only when the tile column changes (tiles are
+    // walked M-fastest, so consecutive tiles of a CTA mostly share their columns).
+    float as_next = 0.0f;
+    if (scaled && static_cast<int>(blockIdx.x) < total_tiles) {
+      const int m_first = (blockIdx.x % p.m_tiles) * kTileM + row_in_tile;
+      if (m_first < p.M) as_next = p.act_scale[m_first];
+    }
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int m0 = (tile % p.m_tiles) * kTileM;
       const int n0 = (tile / p.m_tiles) * p.block_n;
-      if (p.out_dtype != HY3D_S32) {
-        for (int c = et; c < p.block_n; c += kEpiThreads) {
-          const int n = n0 + c;
-          ctrl->ws[buf][c] = n < p.N ? load_scalar(p.w_scale, p.ws_dtype, n) : 0.0f;
-          ctrl->bs[buf][c] = (p.bias && n < p.N) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
+      const float as = as_next;
+      {
+        const int nt = tile + gridDim.x;
+        as_next = 0.0f;
+        if (scaled && nt < total_tiles) {
+          const int mn = (nt % p.m_tiles) * kTileM + row_in_tile;
+          if (mn < p.M) as_next = p.act_scale[mn];
         }
       }
-      epi_bar_sync();
+      if (scaled && n0 != cur_n0) {
+        epi_bar_sync();            // every warp is done reading the previous columns
+        for (int c = et; c < p.block_n; c += kEpiThreads) {
+          const int n = n0 + c;
+          ctrl->ws[c] = n < p.N ? load_scalar(p.w_scale, p.ws_dtype, n) : 0.0f;
+          ctrl->bs[c] = (p.bias && n < p.N) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
+        }
+        epi_bar_sync();
+        cur_n0 = n0;
+      }
       if (ok) ok = mbar_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag,
                              kDevTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) continue;   // warp-uniform; keeps the named-barrier participation count intact
+      if (!ok) continue;   // warp-uniform; the named barriers above stay balanced
       tc_fence_after_sync();
       const int m = m0 + row_in_tile;
       const bool row_ok = m < p.M;
-      const float as = (row_ok && p.out_dtype != HY3D_S32) ? p.act_scale[m] : 0.0f;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(buf * p.acc_cols);
-      const float* wsb = ctrl->ws[buf];
-      const float* bsb = ctrl->bs[buf];
+      const float* wsb = ctrl->ws;
+      const float* bsb = ctrl->bs;
+      bool arrived = false;
       if (p.tma_store) {
         const int nslab = p.block_n / acc_per_slab;
-        for (int s = half; s < nslab; s += 2) {
-          const int c0 = s * acc_per_slab;
-          uint32_t packed[16];
+        const int out_row = m0 + quarter * 32;
+        const bool rows_in = out_row < p.M;
+        const int pend = p.store_bufs - 1;
+        int sb = 0;
+        if (kEpi != HY3D_EPI_GEGLU) {
+          // Software pipeline over this warp's slabs: the tcgen05.ld of the next slab is in
+          // flight while the current one is converted, staged and stored.  Once the last
+          // load has landed the accumulator buffer is handed back to the MMA warp.
+          uint32_t ra[32], rb[32], packed[16];
+          int s = half;
           __syncwarp();
-          if (!geglu) {
-            uint32_t r[32];
-            tmem_ld_x32(t_row + c0, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const float4 w4 = *reinterpret_cast<const float4*>(wsb + c0 + 4 * q);
-              const float4 b4 = *reinterpret_cast<const float4*>(bsb + c0 + 4 * q);
-              float y0 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])), as * w4.x, b4.x);
-              float y1 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 1])), as * w4.y, b4.y);
-              float y2 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])), as * w4.z, b4.z);
-              float y3 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 3])), as * w4.w, b4.w);
-              if (gelu) { y0 = gelu_erf(y0); y1 = gelu_erf(y1); y2 = gelu_erf(y2); y3 = gelu_erf(y3); }
-              packed[2 * q] = pack2(y0, y1, p.out_dtype);
-              packed[2 * q + 1] = pack2(y2, y3, p.out_dtype);
+          if (s < nslab) {
+            tmem_ld_x32(t_row + s * kSlabCols, ra);
+            while (true) {
+              tmem_ld_wait();
+              const int s1 = s + 2;
+              bool last = s1 >= nslab;
+              if (!last) {
+                tmem_ld_x32(t_row + s1 * kSlabCols, rb);
+              } else {
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+                arrived = true;
+              }
+              slab_math<kBf16, kEpi>(ra, as, wsb + s * kSlabCols, bsb + s * kSlabCols, packed);
+              slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o,
+                         (n0 + s * kSlabCols) * 2, out_row, rows_in && n0 + s * kSlabCols < p.N);
+              sb = (sb + 1) % p.store_bufs;
+              if (last) break;
+              tmem_ld_wait();
+              const int s2 = s1 + 2;
+              last = s2 >= nslab;
+              if (!last) {
+                tmem_ld_x32(t_row + s2 * kSlabCols, ra);
+              } else {
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+                arrived = true;
+              }
+              slab_math<kBf16, kEpi>(rb, as, wsb + s1 * kSlabCols, bsb + s1 * kSlabCols, packed);
+              slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o,
+                         (n0 + s1 * kSlabCols) * 2, out_row, rows_in && n0 + s1 * kSlabCols < p.N);
+              sb = (sb + 1) % p.store_bufs;
+              if (last) break;
+              s = s2;
             }
-          } else {
-            // 64 accumulator columns = two blocks of (16 value | 16 gate) -> 32 outputs.
+          }
+        } else {
+          for (int s = half; s < nslab; s += 2) {
+            const int c0 = s * acc_per_slab;
+            uint32_t packed[16];
+            __syncwarp();
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
               uint32_t rv[16], rg[16];
@@ -245,39 +373,11 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
               tmem_ld_x16(t_row + cb, rv);
               tmem_ld_x16(t_row + cb + 16, rg);
               tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 16; j += 2) {
-                float y[2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                  const float v = fmaf(static_cast<float>(static_cast<int32_t>(rv[j + u])),
-                                       as * wsb[cb + j + u], bsb[cb + j + u]);
-                  const float g = fmaf(static_cast<float>(static_cast<int32_t>(rg[j + u])),
-                                       as * wsb[cb + 16 + j + u], bsb[cb + 16 + j + u]);
-                  y[u] = v * gelu_erf(g);
-                }
-                packed[8 * b + (j >> 1)] = pack2(y[0], y[1], p.out_dtype);
-              }
+              slab_math_geglu<kBf16>(rv, rg, as, wsb + cb, bsb + cb, packed + 8 * b);
             }
-          }
-          // The previous TMA store of this warp must have finished reading the staging
-          // buffer before it is overwritten (bulk groups are tracked per issuing thread).
-          if (lane == 0) tma_store_wait_read<0>();
-          __syncwarp();
-          // 32 rows x 64 B, 64-byte swizzle: 16-byte chunk c of row r sits at c ^ ((r >> 1) & 3).
-          const uint32_t row_addr = stage_buf + static_cast<uint32_t>(lane) * 64u;
-          const uint32_t sw = (static_cast<uint32_t>(lane) >> 1) & 3u;
-#pragma unroll
-          for (uint32_t c = 0; c < 4; ++c)
-            st_shared_v4(row_addr + ((c ^ sw) << 4), packed[4 * c], packed[4 * c + 1],
-                         packed[4 * c + 2], packed[4 * c + 3]);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            const int out_col = geglu ? ((n0 + c0) >> 1) : (n0 + c0);
-            const int out_row = m0 + quarter * 32;
-            if (out_col < ldo && out_row < p.M) tma_store_2d(&tm_o, stage_buf, out_col * 2, out_row);
-            tma_store_commit();
+            slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o, ((n0 + c0) >> 1) * 2,
+                       out_row, rows_in && ((n0 + c0) >> 1) < ldo);
+            sb = (sb + 1) % p.store_bufs;
           }
         }
       } else if (!geglu) {
@@ -339,8 +439,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
       }
       __syncwarp();
-      tc_fence_before_sync();
-      mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+      if (!arrived) {
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+      }
     }
     // Global writes of the bulk stores must be complete before the CTA retires.
     if (p.tma_store && lane == 0) tma_store_wait_all<0>();
@@ -410,7 +512,17 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   p.last_ksteps = (k_last + 31) / 32;
   p.tma_store = (out_dtype != HY3D_S32 && block_n % (geglu ? 2 * kSlabCols : kSlabCols) == 0) ? 1 : 0;
   const int stage_bytes = kTileM * kBlockKBytes + block_n * kBlockKBytes;
-  const int fixed = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * kSlabBytes + 1024;
+  // Two staging buffers per epilogue warp unless that costs a pipeline stage below four.
+  int store_bufs = 2;
+  {
+    const int fixed2 = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * 2 * kSlabBytes + 1024;
+    const int fixed1 = fixed2 - kEpiWarps * kSlabBytes;
+    if ((kSmemLimit - fixed2) / stage_bytes < 4 && (kSmemLimit - fixed1) / stage_bytes >= 4)
+      store_bufs = 1;
+    if (const char* e = getenv("HY3D_STORE_BUFS")) store_bufs = atoi(e) == 1 ? 1 : 2;
+  }
+  p.store_bufs = store_bufs;
+  const int fixed = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * store_bufs * kSlabBytes + 1024;
   int stages = (kSmemLimit - fixed) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return HY3D_ERR_SHAPE;
@@ -433,20 +545,29 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
     tm_o = tm_a;   // unused by the kernel
   }
 
-  static bool attr_set[64] = {};
+  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const DenseArgs);
+  static const KernelFn kernels[2][3] = {
+      {gemm_dense_kernel<false, HY3D_EPI_LINEAR>, gemm_dense_kernel<false, HY3D_EPI_GELU>,
+       gemm_dense_kernel<false, HY3D_EPI_GEGLU>},
+      {gemm_dense_kernel<true, HY3D_EPI_LINEAR>, gemm_dense_kernel<true, HY3D_EPI_GELU>,
+       gemm_dense_kernel<true, HY3D_EPI_GEGLU>}};
+  // Raw int32 output runs the direct-store path of the <false, LINEAR> instance.
+  const int ki = out_dtype == HY3D_BF16 ? 1 : 0;
+  const KernelFn kernel = kernels[ki][epilogue];
+  static bool attr_set[64][2][3] = {};
   const int dev = current_device();
   if (dev < 0 || dev >= 64) return HY3D_ERR_CUDA;
-  if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemLimit) != cudaSuccess)
+  if (!attr_set[dev][ki][epilogue]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
+        cudaSuccess)
       return HY3D_ERR_CUDA;
-    attr_set[dev] = true;
+    attr_set[dev][ki][epilogue] = true;
   }
   const int sms = device_sm_count();
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.m_tiles * p.n_tiles;
   const int grid = total_tiles < sms ? total_tiles : sms;
-  gemm_dense_kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_a, tm_b, tm_o, p);
+  kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_a, tm_b, tm_o, p);
   return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
 }
 

@@ -24,8 +24,11 @@ constexpr int kBlockK = 128;         // logical K per stage
 constexpr int kABytes = kTileW * (kBlockK / 2);   // 8192
 constexpr int kEBytes = kTileW * (kBlockK / 8);   // 2048
 constexpr int kMaxStages = 8;
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;
+constexpr int kSlabTokens = 32;                       // tokens per TMA store
+constexpr int kSlabBytes = kSlabTokens * 64;          // 32 tokens x 32 columns x 2 B
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kMaxBlockT = 240;      // 2 * 240 accumulator columns + 4 metadata columns <= 512
 
@@ -36,18 +39,18 @@ struct SparseArgs {
   void* out;
   int ws_dtype, bias_dtype, out_dtype, epilogue;
   int M, N, K;
-  int block_t, stages;
+  int block_t, stages, tma_store;
   int w_tiles, t_tiles, num_kb, last_ksteps;
 };
 
-struct __align__(8) SparseCtrl {
+struct __align__(16) SparseCtrl {
+  float as[2][256];     // per-token activation scales of the current tile, per accumulator buffer
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  float as[2][256];
 };
 
 __device__ __forceinline__ void epi_bar_sync() {
@@ -63,7 +66,8 @@ __device__ __forceinline__ void store_one(void* out, int out_dtype, int64_t idx,
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_e,
-                   const __grid_constant__ CUtensorMap tm_x, const SparseArgs p) {
+                   const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_o,
+                   const SparseArgs p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -72,7 +76,9 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
   const uint32_t b_bytes = static_cast<uint32_t>(p.block_t) * 128u;
   const uint32_t stage_bytes = kABytes + kEBytes + b_bytes;
-  SparseCtrl* ctrl = reinterpret_cast<SparseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes);
+  const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
+  SparseCtrl* ctrl = reinterpret_cast<SparseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes +
+                                                   kEpiWarps * kSlabBytes);
   volatile int* abort_flag = &ctrl->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -95,6 +101,7 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_e);
     tma_prefetch_desc(&tm_x);
+    if (p.tma_store) tma_prefetch_desc(&tm_o);
   }
   if (warp == 1) {
     tmem_alloc_1cta(smem_u32(&ctrl->tmem_base), tmem_cols);
@@ -173,11 +180,14 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
   } else {
     // ---------------- epilogue ----------------
-    const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;   // weight row within the tile
+    const int quarter = warp & 3;                   // tensor-memory lane quarter
+    const int half = (warp - 2) >> 2;               // which of the two warps sharing it
+    const int row_in_tile = quarter * 32 + lane;    // weight row within the tile
     const int et = threadIdx.x - 64;
     const bool geglu = p.epilogue == HY3D_EPI_GEGLU;
+    const bool gelu = p.epilogue == HY3D_EPI_GELU;
     const int64_t ldo = geglu ? (p.N >> 1) : p.N;
+    const uint32_t stage_buf = staging_base + static_cast<uint32_t>(warp - 2) * kSlabBytes;
     bool ok = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
@@ -204,38 +214,91 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(buf * p.block_t);
-      // GEGLU: weight rows come in blocks of 32 = 16 value rows then their 16 gate rows, so
-      // lanes 0-15 hold values and lanes 16-31 the matching gates.
-      const int64_t out_col = geglu ? ((w0 + quarter * 32) >> 1) + (lane & 15) : n;
-      for (int c = 0; c < p.block_t; c += 16) {
-        uint32_t r[16];
-        __syncwarp();
-        tmem_ld_x16(t_row + c, r);
-        tmem_ld_wait();
-        if (p.out_dtype == HY3D_S32) {
-          if (n_ok) {
+      const float* asb = ctrl->as[buf];
+      if (p.tma_store) {
+        // Slabs of 32 tokens; this thread owns output column n, the warp 32 adjacent columns,
+        // so a slab is a 32 (tokens) x 64 B block of the output, staged with 64-byte swizzle.
+        const int nslab = p.block_t / kSlabTokens;
+        const uint32_t chunk = static_cast<uint32_t>(lane) >> 3;
+        const uint32_t in_chunk = (static_cast<uint32_t>(lane) & 7u) * 2u;
+        for (int s = half; s < nslab; s += 2) {
+          const int c0 = s * kSlabTokens;
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_x32(t_row + c0, r);
+          tmem_ld_wait();
+          float y[32];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 a4 = *reinterpret_cast<const float4*>(asb + c0 + 4 * q);
+            y[4 * q + 0] = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])), a4.x * ws, bs);
+            y[4 * q + 1] = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 1])), a4.y * ws, bs);
+            y[4 * q + 2] = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])), a4.z * ws, bs);
+            y[4 * q + 3] = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 3])), a4.w * ws, bs);
+          }
+          if (gelu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = gelu_erf(y[j]);
+          }
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            // token row j of the slab: 64 B; 16-byte chunk c sits at c ^ ((j >> 1) & 3)
+            const uint32_t addr = stage_buf + static_cast<uint32_t>(j) * 64u +
+                                  ((chunk ^ ((static_cast<uint32_t>(j) >> 1) & 3u)) << 4) + in_chunk;
+            uint16_t h;
+            if (p.out_dtype == HY3D_BF16) {
+              __nv_bfloat16 v = __float2bfloat16_rn(y[j]);
+              h = *reinterpret_cast<uint16_t*>(&v);
+            } else {
+              __half v = __float2half_rn(y[j]);
+              h = *reinterpret_cast<uint16_t*>(&v);
+            }
+            asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(h) : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int out_col = w0 + quarter * 32;
+            const int out_row = t0 + c0;
+            if (out_col < p.N && out_row < p.M) tma_store_2d(&tm_o, stage_buf, out_col * 2, out_row);
+            tma_store_commit();
+          }
+        }
+      } else {
+        // GEGLU: weight rows come in blocks of 32 = 16 value rows then their 16 gate rows, so
+        // lanes 0-15 hold values and lanes 16-31 the matching gates.
+        const int64_t out_col = geglu ? ((w0 + quarter * 32) >> 1) + (lane & 15) : n;
+        for (int c = 16 * half; c < p.block_t; c += 32) {
+          uint32_t r[16];
+          __syncwarp();
+          tmem_ld_x16(t_row + c, r);
+          tmem_ld_wait();
+          if (p.out_dtype == HY3D_S32) {
+            if (n_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int t = t0 + c + j;
+                if (t < p.M)
+                  reinterpret_cast<int32_t*>(p.out)[static_cast<int64_t>(t) * ldo + n] =
+                      static_cast<int32_t>(r[j]);
+              }
+            }
+          } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = t0 + c + j;
-              if (t < p.M)
-                reinterpret_cast<int32_t*>(p.out)[static_cast<int64_t>(t) * ldo + n] =
-                    static_cast<int32_t>(r[j]);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c + j;
-            float y = fmaf(static_cast<float>(static_cast<int32_t>(r[j])), ctrl->as[buf][c + j] * ws,
-                           bs);
-            if (p.epilogue == HY3D_EPI_GELU) y = gelu_erf(y);
-            if (geglu) {
-              const float g = __shfl_down_sync(0xffffffffu, y, 16);
-              y = y * gelu_erf(g);
-              if (lane < 16 && n_ok && t < p.M)
+              float y = fmaf(static_cast<float>(static_cast<int32_t>(r[j])), asb[c + j] * ws, bs);
+              if (gelu) y = gelu_erf(y);
+              if (geglu) {
+                const float g = __shfl_down_sync(0xffffffffu, y, 16);
+                y = y * gelu_erf(g);
+                if (lane < 16 && n_ok && t < p.M)
+                  store_one(p.out, p.out_dtype, static_cast<int64_t>(t) * ldo + out_col, y);
+              } else if (n_ok && t < p.M) {
                 store_one(p.out, p.out_dtype, static_cast<int64_t>(t) * ldo + out_col, y);
-            } else if (n_ok && t < p.M) {
-              store_one(p.out, p.out_dtype, static_cast<int64_t>(t) * ldo + out_col, y);
+              }
             }
           }
         }
@@ -244,6 +307,7 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
     }
+    if (p.tma_store && lane == 0) tma_store_wait_all<0>();
   }
 
   // ---------------- teardown ----------------
@@ -267,9 +331,7 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
                   const uint32_t* w_meta, int64_t meta_ld, const void* w_scale, int ws_dtype,
                   const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
                   int64_t K, int epilogue, int block_t, cudaStream_t stream) {
-  if (!X || !w_comp || !w_meta || !out) return HY3D_ERR_ARG;
   if (out_dtype != HY3D_F16 && out_dtype != HY3D_BF16 && out_dtype != HY3D_S32) return HY3D_ERR_ARG;
-  if (out_dtype != HY3D_S32 && (!act_scale || !w_scale)) return HY3D_ERR_ARG;
   if (epilogue < HY3D_EPI_LINEAR || epilogue > HY3D_EPI_GEGLU) return HY3D_ERR_ARG;
   if (out_dtype == HY3D_S32 && epilogue != HY3D_EPI_LINEAR) return HY3D_ERR_ARG;
   if (ws_dtype < HY3D_F16 || ws_dtype > HY3D_F32) return HY3D_ERR_ARG;
@@ -279,10 +341,12 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   if (epilogue == HY3D_EPI_GEGLU && (N & 31)) return HY3D_ERR_SHAPE;
   const int64_t kblocks = (K + kBlockK - 1) / kBlockK;
   if (meta_ld != 4 * kblocks) return HY3D_ERR_SHAPE;
+  if (M == 0) return HY3D_OK;
+  if (!X || !w_comp || !w_meta || !out) return HY3D_ERR_ARG;
+  if (out_dtype != HY3D_S32 && (!act_scale || !w_scale)) return HY3D_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(w_comp) |
        reinterpret_cast<uintptr_t>(w_meta) | reinterpret_cast<uintptr_t>(out)) & 15)
     return HY3D_ERR_SHAPE;
-  if (M == 0) return HY3D_OK;
 
   if (block_t == 0) {
     block_t = 192;
@@ -301,7 +365,8 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   const int k_last = static_cast<int>(K - (kblocks - 1) * kBlockK);
   p.last_ksteps = (k_last + 63) / 64;
   const int stage_bytes = kABytes + kEBytes + block_t * 128;
-  const int fixed = static_cast<int>(sizeof(SparseCtrl)) + 1024;
+  p.tma_store = (out_dtype != HY3D_S32 && epilogue != HY3D_EPI_GEGLU && block_t % kSlabTokens == 0) ? 1 : 0;
+  const int fixed = static_cast<int>(sizeof(SparseCtrl)) + kEpiWarps * kSlabBytes + 1024;
   int stages = (kSmemLimit - fixed) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return HY3D_ERR_SHAPE;
@@ -311,7 +376,7 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   int smem_bytes = stages * stage_bytes + fixed;
   if (smem_bytes < 120 * 1024) smem_bytes = 120 * 1024;
 
-  CUtensorMap tm_w, tm_e, tm_x;
+  CUtensorMap tm_w, tm_e, tm_x, tm_o;
   int rc = encode_tmap_2d_u8(&tm_w, w_comp, static_cast<uint64_t>(K / 2), static_cast<uint64_t>(N),
                              static_cast<uint64_t>(K / 2), kBlockK / 2, kTileW, 64);
   if (rc != HY3D_OK) return rc;
@@ -321,6 +386,15 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   rc = encode_tmap_2d_u8(&tm_x, X, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
                          static_cast<uint64_t>(K), kBlockK, static_cast<uint32_t>(block_t), 128);
   if (rc != HY3D_OK) return rc;
+
+  if (p.tma_store) {
+    const uint64_t row_bytes = static_cast<uint64_t>(N) * 2;
+    rc = encode_tmap_2d_u8(&tm_o, out, row_bytes, static_cast<uint64_t>(M), row_bytes, 64,
+                           kSlabTokens, 64);
+    if (rc != HY3D_OK) return rc;
+  } else {
+    tm_o = tm_x;   // unused by the kernel
+  }
 
   static bool attr_set[64] = {};
   const int dev = current_device();
@@ -335,7 +409,7 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.w_tiles * p.t_tiles;
   const int grid = total_tiles < sms ? total_tiles : sms;
-  gemm_sparse_kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_w, tm_e, tm_x, p);
+  gemm_sparse_kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_w, tm_e, tm_x, tm_o, p);
   return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
 }
 
