@@ -33,6 +33,9 @@ SIGNATURES = {
     "hy3d_linear_w8a8_dense": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64,
                                c_int, c_int, c_int, c_void_p],
+    "hy3d_linear_w8a8_dense_static": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p,
+                                      c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int,
+                                      c_void_p],
     "hy3d_prune_pack_24": [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64,
                            c_void_p],
     "hy3d_gemm_w8a8_sparse24": [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int,
@@ -54,6 +57,9 @@ def configure(lib: ctypes.CDLL) -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = argtypes
         fn.restype = c_int
+    for name in ("hy3d_static_scratch_max_bytes", "hy3d_static_scratch_max_rows"):
+        getattr(lib, name).restype = c_int64
+        getattr(lib, name).argtypes = []
     lib.hy3d_arch.restype = ctypes.c_char_p
     lib.hy3d_arch.argtypes = []
     lib.hy3d_status_string.restype = ctypes.c_char_p
@@ -201,6 +207,26 @@ class TcGemmModule(_Base):
                 w_int8.data_ptr(), w_scale.data_ptr(), _DTYPE_CODE[w_scale.dtype], bptr, bcode,
                 out.data_ptr(), _DTYPE_CODE[x.dtype], M, N, K, epilogue, cta_group, block_n,
                 self._stream(x)), "hy3d_linear_w8a8_dense")
+        return out
+
+    def int8_linear_tc_static(self, x, w_int8, w_scale, bias, out=None, epilogue=EPI_LINEAR):
+        """``int8_linear_tc`` through the entry point that keeps its scratch inside the
+        library, for callers that cannot allocate where the layer runs.  Pass ``out`` to make
+        the call itself allocation-free; M*K and M are limited (see the header)."""
+        self._req(x, "x", (torch.float16, torch.bfloat16), 2)
+        self._req(w_int8, "w_int8", torch.int8, 2)
+        M, K = x.shape
+        N = w_int8.shape[0]
+        if w_int8.shape[1] != K:
+            raise RuntimeError(f"K mismatch: x has {K}, w_int8 has {w_int8.shape[1]}")
+        if out is None:
+            out = torch.empty(self._out_shape(M, N, epilogue), dtype=x.dtype, device=x.device)
+        bptr, bcode = self._opt_bias(bias)
+        with torch.cuda.device(x.device):
+            self._check(self._lib.hy3d_linear_w8a8_dense_static(
+                x.data_ptr(), _DTYPE_CODE[x.dtype], K, w_int8.data_ptr(), w_scale.data_ptr(),
+                _DTYPE_CODE[w_scale.dtype], bptr, bcode, out.data_ptr(), _DTYPE_CODE[out.dtype],
+                M, N, K, epilogue, self._stream(x)), "hy3d_linear_w8a8_dense_static")
         return out
 
     def test_mma(self, a, b):

@@ -5,3 +5,4 @@
 #include "gemm_dense.cu"
 #include "gemm_sparse.cu"
 #include "capi.cu"
+#include "static_scratch.cu"

@@ -96,6 +96,31 @@ int hy3d_linear_w8a8_dense(const void* x, int x_dtype, int64_t ldx,
                            int epilogue, int cta_group, int block_n, void* stream);
 
 /*
+ * The dense linear layer again, for callers that may not allocate device memory where the
+ * layer runs (an allocation-free region of a render or capture loop, a sandboxed plugin that
+ * is only handed pre-registered buffers, a process whose device pool belongs to another
+ * runtime): the two scratch buffers hy3d_linear_w8a8_dense asks for live in a fixed array
+ * inside the library instead, so only inputs and outputs are passed.  No counterpart in the
+ * reference, whose extension allocates its scratch through torch on every call.
+ * Limits: M * K <= hy3d_static_scratch_max_bytes() (16 MiB) and
+ * M <= hy3d_static_scratch_max_rows() (65536); beyond them the call returns
+ * HY3D_ERR_TOO_LARGE and launches nothing.  Every GPU that loads the library holds that array
+ * (16.25 MiB) until the process exits.  Calls on one device share it: run them on one stream,
+ * since calls whose kernels overlap on the GPU race on it.  Its contents carry over between
+ * calls, which is harmless: each call overwrites everything it later reads.  The first call on
+ * a device looks up the array's device address; make that call before any stream capture.
+ * Tile shape and CTA grouping are chosen by the library (as with 0 / 0 in the regular call).
+ */
+int hy3d_linear_w8a8_dense_static(const void* x, int x_dtype, int64_t ldx,
+                                  const int8_t* B, const void* w_scale, int w_scale_dtype,
+                                  const void* bias, int bias_dtype,
+                                  void* out, int out_dtype,
+                                  int64_t M, int64_t N, int64_t K,
+                                  int epilogue, void* stream);
+int64_t hy3d_static_scratch_max_bytes(void);
+int64_t hy3d_static_scratch_max_rows(void);
+
+/*
  * Offline 2:4 prune + compress + metadata pack of an int8 weight matrix, one pass.
  * Per group of 4 along K the two smallest |w| are dropped; the tie rule is
  *   min1=0,min2=1; if |w0|>|w1| swap; for i in 2,3: if |wi|<|w[min1]| {min2=min1;min1=i}

@@ -28,7 +28,8 @@ def test_library_exports_every_declared_symbol(build_mod):
 def test_binding_table_covers_header(build_mod):
     binding = __import__("importlib").import_module("hunyuan3d-tools_b200.csrc._binding")
     declared = set(_declared_symbols())
-    bound = set(binding.SIGNATURES) | {"hy3d_arch", "hy3d_status_string"}
+    bound = set(binding.SIGNATURES) | {"hy3d_arch", "hy3d_status_string",
+                                       "hy3d_static_scratch_max_bytes", "hy3d_static_scratch_max_rows"}
     assert declared == bound
 
 
