@@ -101,6 +101,18 @@ using namespace hy3d;
 
 extern "C" {
 
+#ifdef HY3D_TRACE
+// Diagnostic builds only: copies out and clears the timeline of the traced CTA.
+int hy3d_trace_read(unsigned long long* out, int next_cta) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, g_trace_buf, 4 * 4096 * sizeof(unsigned long long));
+  static unsigned long long zeros[4 * 4096];
+  cudaMemcpyToSymbol(g_trace_buf, zeros, sizeof(zeros));
+  cudaMemcpyToSymbol(g_trace_cta, &next_cta, sizeof(int));
+  return 0;
+}
+#endif
+
 int hy3d_version(void) { return 100; }
 const char* hy3d_arch(void) { return "sm_100a"; }
 

@@ -20,6 +20,32 @@ namespace hy3d {
 // ------------------------------------------------------------------------------------
 __device__ int g_device_status = 0;
 
+// Optional timeline tracing of one CTA (compiled in only with -DHY3D_TRACE; never part of
+// the shipped library).  Each record: SM clock << 16 | event << 8 | argument.
+#ifdef HY3D_TRACE
+__device__ unsigned long long g_trace_buf[4 * 4096];
+__device__ int g_trace_cta = 0;
+// Store-only (no atomics, nothing to wait for): every role keeps its own record counter
+// in a register and owns a 4096-entry slice of the buffer.
+__device__ __forceinline__ void trace_event(int role, unsigned& idx, int ev, int arg) {
+  if (idx < 4096u)
+    g_trace_buf[role * 4096 + idx] = (static_cast<unsigned long long>(clock64()) << 16) |
+                                     (static_cast<unsigned long long>(ev & 0xFF) << 8) | (arg & 0xFF);
+  ++idx;
+}
+#define HY3D_TRACE_DECL(name) unsigned name = (static_cast<int>(blockIdx.x) == g_trace_cta) ? 0u : 4096u
+#define HY3D_TRACE_EVENT(role, idx, ev, arg) trace_event(role, idx, ev, arg)
+#ifdef HY3D_TRACE_PER_STAGE
+#define HY3D_TRACE_FINE(role, idx, ev, arg) trace_event(role, idx, ev, arg)
+#else
+#define HY3D_TRACE_FINE(role, idx, ev, arg) ((void)0)
+#endif
+#else
+#define HY3D_TRACE_DECL(name) ((void)0)
+#define HY3D_TRACE_EVENT(role, idx, ev, arg) ((void)0)
+#define HY3D_TRACE_FINE(role, idx, ev, arg) ((void)0)
+#endif
+
 enum DeviceError : int {
   kDevOk = 0,
   kDevTimeoutFull = 101,       // consumer gave up waiting for a TMA stage
@@ -92,6 +118,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking probe.  try_wait may park the thread and was measured to hand control back
+// only a few hundred nanoseconds after the phase completes; polling with test_wait reacts
+// within tens of cycles, which matters for the per-stage handshakes of the GEMM pipelines.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -111,15 +151,18 @@ constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
 
 // Bounded wait.  `abort_flag` lives in shared memory and is set by whichever role times
 // out first, so the other roles leave their waits promptly.  Returns false on give-up.
-template <bool kCluster = false>
+// Bounded wait.  `abort_flag` lives in shared memory and is set by whichever role times
+// out first, so the other roles leave their waits promptly.  Returns false on give-up.
+// kSpin selects test_wait polling (lowest wake-up latency) instead of the parking try_wait.
+template <bool kSpin = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int err_code) {
-  if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+  if (kSpin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
-    if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xFF) == 0) {
+    if (kSpin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    if ((++spins & (kSpin ? 0xFFFu : 0xFFu)) == 0) {
       if (*abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
@@ -145,6 +188,30 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y)
       : "memory");
+}
+// CTA-pair form: the data lands in this CTA's shared memory, the completion bytes are
+// credited to `bar_cluster`, a shared::cluster address that may name the pair's other CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* m,
+                                                 uint32_t bar_cluster, int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int32_t x,
                                              int32_t y) {

@@ -47,6 +47,7 @@ struct DenseArgs {
   int M, N, K;
   int block_n, stages, acc_cols, tma_store, store_bufs;
   int m_tiles, n_tiles, num_kb, last_ksteps;
+  int debug;   // diagnostic switches (HY3D_DEBUG): 1 no TMA loads, 2 no epilogue work, 4 no MMA
 };
 
 struct __align__(16) DenseCtrl {
@@ -145,7 +146,7 @@ __device__ __forceinline__ void slab_store(const uint32_t (&packed)[16], uint32_
   }
 }
 
-template <bool kBf16, int kEpi>
+template <bool kBf16, int kEpi, int kG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_o, const DenseArgs p) {
@@ -156,7 +157,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const uint32_t smem_base = raw_addr + pad;
 
   const uint32_t a_bytes = kTileM * kBlockKBytes;
-  const uint32_t b_bytes = static_cast<uint32_t>(p.block_n) * kBlockKBytes;
+  // With a CTA pair (kG == 2) each CTA stages its own 128 rows of A and half of the B tile.
+  const uint32_t b_bytes = static_cast<uint32_t>(p.block_n / kG) * kBlockKBytes;
   const uint32_t stage_bytes = a_bytes + b_bytes;
   const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
   DenseCtrl* ctrl = reinterpret_cast<DenseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes +
@@ -165,7 +167,13 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int total_tiles = p.m_tiles * p.n_tiles;     // m_tiles counts 128*kG-row units
+  const uint32_t cta_rank = kG == 2 ? cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0;                 // issues the MMAs for the pair
+  const int first_tile = static_cast<int>(blockIdx.x) / kG;
+  const int tile_step = static_cast<int>(gridDim.x) / kG;
+  const int row_off = static_cast<int>(cta_rank) * kTileM;
+  const int col_off = static_cast<int>(cta_rank) * (p.block_n / kG);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -174,7 +182,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
-      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kEpiThreads);
+      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kG * kEpiThreads);
     }
     ctrl->abort_flag = 0;
     fence_barrier_init();
@@ -183,76 +191,110 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (p.tma_store) tma_prefetch_desc(&tm_o);
   }
   if (warp == 1) {
-    tmem_alloc_1cta(smem_u32(&ctrl->tmem_base), static_cast<uint32_t>(2 * p.acc_cols));
-    tmem_relinquish_1cta();
+    if (kG == 2) {
+      tmem_alloc_2cta(smem_u32(&ctrl->tmem_base), static_cast<uint32_t>(2 * p.acc_cols));
+      tmem_relinquish_2cta();
+    } else {
+      tmem_alloc_1cta(smem_u32(&ctrl->tmem_base), static_cast<uint32_t>(2 * p.acc_cols));
+      tmem_relinquish_1cta();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (kG == 2) cluster_sync_all();   // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
+  HY3D_TRACE_DECL(tr);
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const int m0 = (tile % p.m_tiles) * kTileM;
-      const int n0 = (tile / p.m_tiles) * p.block_n;
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0) {
+    // ---------------- TMA producer (one thread) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+        const int m0 = (tile % p.m_tiles) * (kTileM * kG) + row_off;
+        const int n0 = (tile / p.m_tiles) * p.block_n + col_off;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
+          if (!ok) break;
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_base + stage * stage_bytes;
-          mbar_arrive_expect_tx(full, stage_bytes);
-          tma_load_2d(sa, &tm_a, full, kb * kBlockKBytes, m0);
-          tma_load_2d(sa + a_bytes, &tm_b, full, kb * kBlockKBytes, n0);
+          if (p.debug & 1) {
+            if (leader) mbar_arrive(full);
+          } else if (kG == 1) {
+            mbar_arrive_expect_tx(full, stage_bytes);
+            tma_load_2d(sa, &tm_a, full, kb * kBlockKBytes, m0);
+            tma_load_2d(sa + a_bytes, &tm_b, full, kb * kBlockKBytes, n0);
+          } else {
+            // Both CTAs credit their bytes to the leader's barrier; only the leader arrives.
+            const uint32_t full_leader = map_to_cta(full, 0);
+            if (leader) mbar_arrive_expect_tx(full, 2 * stage_bytes);
+            tma_load_2d_pair(sa, &tm_a, full_leader, kb * kBlockKBytes, m0);
+            tma_load_2d_pair(sa + a_bytes, &tm_b, full_leader, kb * kBlockKBytes, n0);
+          }
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
-        __syncwarp();
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    const uint32_t idesc = make_idesc_i8(kTileM, static_cast<uint32_t>(p.block_n), false);
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    int it = 0;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-      const int buf = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
-                     kDevTimeoutTmemEmpty);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.acc_cols);
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, kDevTimeoutFull);
-        ok = __all_sync(0xffffffffu, ok);
+    // ---------------- MMA issuer (one thread of the pair's leader CTA) ----------------
+    // The tensor pipe accepts an MMA only when it can start it, so every cycle this thread
+    // spends between two issues is a cycle the pipe idles: the loop is kept to one barrier
+    // probe, four issues and one commit per stage.
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_i8(kTileM * kG, static_cast<uint32_t>(p.block_n), false);
+      const uint64_t desc_hi = make_smem_desc(0, 1024, 128);      // everything but the address
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
+                       kDevTimeoutTmemEmpty);
         if (!ok) break;
         tc_fence_after_sync();
-        if (lane == 0) {
+        HY3D_TRACE_EVENT(1, tr, 6, it);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.acc_cols);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, kDevTimeoutFull);
+          if (!ok) break;
           const uint32_t sa = smem_base + stage * stage_bytes;
-          const uint64_t da = make_smem_desc(sa, 1024, 128);
-          const uint64_t db = make_smem_desc(sa + a_bytes, 1024, 128);
+          // Each K step of 32 int8 is 32 bytes further along the swizzled row: +2 in the
+          // descriptor's 16-byte address units.
+          const uint64_t da = desc_hi | static_cast<uint64_t>((sa & 0x3FFFFu) >> 4);
+          const uint64_t db = desc_hi | static_cast<uint64_t>(((sa + a_bytes) & 0x3FFFFu) >> 4);
           const int nk = (kb == p.num_kb - 1) ? p.last_ksteps : 4;
-          for (int k = 0; k < nk; ++k) {
-            // Each K step of 32 int8 is 32 bytes further along the swizzled row: +2 in the
-            // descriptor's 16-byte address units.
-            mma_i8_1cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          if (!(p.debug & 4)) {
+            if (nk == 4) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                if (kG == 1) mma_i8_1cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                else mma_i8_2cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              }
+            } else {
+              for (int k = 0; k < nk; ++k) {
+                if (kG == 1) mma_i8_1cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                else mma_i8_2cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              }
+            }
           }
-          tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
+          // Frees the stage (in both CTAs of a pair) once these MMAs have read it.
+          if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
+          else tc_commit_2cta(smem_u32(&ctrl->empty[stage]), 3);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
-        __syncwarp();
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        if (ok) {
+          HY3D_TRACE_EVENT(1, tr, 3, it);
+          if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
+          else tc_commit_2cta(smem_u32(&ctrl->tmem_full[buf]), 3);
+        }
       }
-      if (ok && lane == 0) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;            // tensor-memory lane quarter this warp may read
@@ -264,6 +306,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int64_t ldo = geglu ? (p.N >> 1) : p.N;
     const uint32_t stage_buf = staging_base + static_cast<uint32_t>((warp - 2) * p.store_bufs) * kSlabBytes;
     const int acc_per_slab = geglu ? 2 * kSlabCols : kSlabCols;
+    // The accumulator buffer is handed back to the leader's MMA warp (its own CTA or the peer).
+    auto release_acc = [&](uint32_t bar) {
+      if (kG == 1 || leader) mbar_arrive(bar); else mbar_arrive_cluster(bar, 0);
+    };
     bool ok = true;
     int it = 0;
     int cur_n0 = -1;
@@ -272,21 +318,21 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // per-column scales / bias are refilled only when the tile column changes (tiles are
     // walked M-fastest, so consecutive tiles of a CTA mostly share their columns).
     float as_next = 0.0f;
-    if (scaled && static_cast<int>(blockIdx.x) < total_tiles) {
-      const int m_first = (blockIdx.x % p.m_tiles) * kTileM + row_in_tile;
+    if (scaled && first_tile < total_tiles) {
+      const int m_first = (first_tile % p.m_tiles) * (kTileM * kG) + row_off + row_in_tile;
       if (m_first < p.M) as_next = p.act_scale[m_first];
     }
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (tile % p.m_tiles) * kTileM;
+      const int m0 = (tile % p.m_tiles) * (kTileM * kG) + row_off;
       const int n0 = (tile / p.m_tiles) * p.block_n;
       const float as = as_next;
       {
-        const int nt = tile + gridDim.x;
+        const int nt = tile + tile_step;
         as_next = 0.0f;
         if (scaled && nt < total_tiles) {
-          const int mn = (nt % p.m_tiles) * kTileM + row_in_tile;
+          const int mn = (nt % p.m_tiles) * (kTileM * kG) + row_off + row_in_tile;
           if (mn < p.M) as_next = p.act_scale[mn];
         }
       }
@@ -305,6 +351,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) continue;   // warp-uniform; the named barriers above stay balanced
       tc_fence_after_sync();
+      if (threadIdx.x == 64) HY3D_TRACE_EVENT(2, tr, 4, it);
       const int m = m0 + row_in_tile;
       const bool row_ok = m < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
@@ -312,7 +359,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const float* wsb = ctrl->ws;
       const float* bsb = ctrl->bs;
       bool arrived = false;
-      if (p.tma_store) {
+      if (p.tma_store && !(p.debug & 2)) {
         const int nslab = p.block_n / acc_per_slab;
         const int out_row = m0 + quarter * 32;
         const bool rows_in = out_row < p.M;
@@ -335,7 +382,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 tmem_ld_x32(t_row + s1 * kSlabCols, rb);
               } else {
                 tc_fence_before_sync();
-                mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+                release_acc(smem_u32(&ctrl->tmem_empty[buf]));
                 arrived = true;
               }
               slab_math<kBf16, kEpi>(ra, as, wsb + s * kSlabCols, bsb + s * kSlabCols, packed);
@@ -350,7 +397,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 tmem_ld_x32(t_row + s2 * kSlabCols, ra);
               } else {
                 tc_fence_before_sync();
-                mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+                release_acc(smem_u32(&ctrl->tmem_empty[buf]));
                 arrived = true;
               }
               slab_math<kBf16, kEpi>(rb, as, wsb + s1 * kSlabCols, bsb + s1 * kSlabCols, packed);
@@ -380,6 +427,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             sb = (sb + 1) % p.store_bufs;
           }
         }
+      } else if (p.tma_store) {
+        // diagnostic run: epilogue work skipped
       } else if (!geglu) {
         for (int c = 16 * half; c < p.block_n; c += 32) {
           uint32_t r[16];
@@ -438,10 +487,11 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           }
         }
       }
+      if (threadIdx.x == 64) HY3D_TRACE_EVENT(2, tr, 5, it);
       __syncwarp();
       if (!arrived) {
         tc_fence_before_sync();
-        mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+        release_acc(smem_u32(&ctrl->tmem_empty[buf]));
       }
     }
     // Global writes of the bulk stores must be complete before the CTA retires.
@@ -457,9 +507,13 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     while (global_timer_ns() - t0 < 200000ull) { }
     __syncthreads();
   }
+  // Neither CTA of a pair may retire while the other can still touch its shared memory,
+  // barriers or tensor memory.
+  if (kG == 2) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc_1cta(tmem_base, static_cast<uint32_t>(2 * p.acc_cols));
+    if (kG == 2) tmem_dealloc_2cta(tmem_base, static_cast<uint32_t>(2 * p.acc_cols));
+    else tmem_dealloc_1cta(tmem_base, static_cast<uint32_t>(2 * p.acc_cols));
   }
 }
 
@@ -497,6 +551,16 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   if (block_n < 16 || block_n > 256 || (block_n & 15) || (geglu && (block_n & 31)))
     return HY3D_ERR_SHAPE;
 
+  // CTA pairs need an even split of the B tile into two multiples of 16 rows.
+  int group = cta_group;
+  if (group == 0) {
+    if (const char* e = getenv("HY3D_CTA_GROUP")) group = atoi(e) == 2 ? 2 : 1; else group = 1;
+  }
+  if (group == 2 && (block_n & 31)) {
+    if (cta_group == 2) return HY3D_ERR_SHAPE;
+    group = 1;
+  }
+
   DenseArgs p;
   p.act_scale = act_scale; p.w_scale = w_scale; p.bias = bias; p.out = out;
   p.ws_dtype = ws_dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype; p.epilogue = epilogue;
@@ -505,13 +569,13 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   int acc_cols = 32;
   while (acc_cols < block_n) acc_cols <<= 1;
   p.acc_cols = acc_cols;
-  p.m_tiles = static_cast<int>((M + kTileM - 1) / kTileM);
+  p.m_tiles = static_cast<int>((M + kTileM * group - 1) / (kTileM * group));
   p.n_tiles = static_cast<int>((N + block_n - 1) / block_n);
   p.num_kb = static_cast<int>((K + kBlockKBytes - 1) / kBlockKBytes);
   const int k_last = static_cast<int>(K - static_cast<int64_t>(p.num_kb - 1) * kBlockKBytes);
   p.last_ksteps = (k_last + 31) / 32;
   p.tma_store = (out_dtype != HY3D_S32 && block_n % (geglu ? 2 * kSlabCols : kSlabCols) == 0) ? 1 : 0;
-  const int stage_bytes = kTileM * kBlockKBytes + block_n * kBlockKBytes;
+  const int stage_bytes = kTileM * kBlockKBytes + (block_n / group) * kBlockKBytes;
   // Two staging buffers per epilogue warp unless that costs a pipeline stage below four.
   int store_bufs = 2;
   {
@@ -525,8 +589,10 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   const int fixed = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * store_bufs * kSlabBytes + 1024;
   int stages = (kSmemLimit - fixed) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
+  if (const char* e = getenv("HY3D_STAGES")) { const int v = atoi(e); if (v >= 2 && v < stages) stages = v; }
   if (stages < 2) return HY3D_ERR_SHAPE;
   p.stages = stages;
+  { const char* e = getenv("HY3D_DEBUG"); p.debug = e ? atoi(e) : 0; }
   const int smem_bytes = stages * stage_bytes + fixed;
 
   CUtensorMap tm_a, tm_b, tm_o;
@@ -534,7 +600,8 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
                              static_cast<uint64_t>(K), kBlockKBytes, kTileM, 128);
   if (rc != HY3D_OK) return rc;
   rc = encode_tmap_2d_u8(&tm_b, B, static_cast<uint64_t>(K), static_cast<uint64_t>(N),
-                         static_cast<uint64_t>(K), kBlockKBytes, static_cast<uint32_t>(block_n), 128);
+                         static_cast<uint64_t>(K), kBlockKBytes,
+                         static_cast<uint32_t>(block_n / group), 128);
   if (rc != HY3D_OK) return rc;
   if (p.tma_store) {
     const uint64_t row_bytes = static_cast<uint64_t>(geglu ? N / 2 : N) * 2;
@@ -546,28 +613,48 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   }
 
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const DenseArgs);
-  static const KernelFn kernels[2][3] = {
-      {gemm_dense_kernel<false, HY3D_EPI_LINEAR>, gemm_dense_kernel<false, HY3D_EPI_GELU>,
-       gemm_dense_kernel<false, HY3D_EPI_GEGLU>},
-      {gemm_dense_kernel<true, HY3D_EPI_LINEAR>, gemm_dense_kernel<true, HY3D_EPI_GELU>,
-       gemm_dense_kernel<true, HY3D_EPI_GEGLU>}};
+  static const KernelFn kernels[2][2][3] = {
+      {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, 1>, gemm_dense_kernel<false, HY3D_EPI_GELU, 1>,
+        gemm_dense_kernel<false, HY3D_EPI_GEGLU, 1>},
+       {gemm_dense_kernel<true, HY3D_EPI_LINEAR, 1>, gemm_dense_kernel<true, HY3D_EPI_GELU, 1>,
+        gemm_dense_kernel<true, HY3D_EPI_GEGLU, 1>}},
+      {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, 2>, gemm_dense_kernel<false, HY3D_EPI_GELU, 2>,
+        gemm_dense_kernel<false, HY3D_EPI_GEGLU, 2>},
+       {gemm_dense_kernel<true, HY3D_EPI_LINEAR, 2>, gemm_dense_kernel<true, HY3D_EPI_GELU, 2>,
+        gemm_dense_kernel<true, HY3D_EPI_GEGLU, 2>}}};
   // Raw int32 output runs the direct-store path of the <false, LINEAR> instance.
   const int ki = out_dtype == HY3D_BF16 ? 1 : 0;
-  const KernelFn kernel = kernels[ki][epilogue];
-  static bool attr_set[64][2][3] = {};
+  const KernelFn kernel = kernels[group - 1][ki][epilogue];
+  static bool attr_set[64][2][2][3] = {};
   const int dev = current_device();
   if (dev < 0 || dev >= 64) return HY3D_ERR_CUDA;
-  if (!attr_set[dev][ki][epilogue]) {
+  if (!attr_set[dev][group - 1][ki][epilogue]) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
         cudaSuccess)
       return HY3D_ERR_CUDA;
-    attr_set[dev][ki][epilogue] = true;
+    attr_set[dev][group - 1][ki][epilogue] = true;
   }
   const int sms = device_sm_count();
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.m_tiles * p.n_tiles;
-  const int grid = total_tiles < sms ? total_tiles : sms;
-  kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_a, tm_b, tm_o, p);
+  const int max_clusters = sms / group;
+  const int grid = group * (total_tiles < max_clusters ? total_tiles : max_clusters);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(group);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_o, p) != cudaSuccess) {
+    cudaGetLastError();
+    return HY3D_ERR_CUDA;
+  }
   return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
 }
 

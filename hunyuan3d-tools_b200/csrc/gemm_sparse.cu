@@ -4,14 +4,14 @@
 // tile on the 128 tensor-memory lanes); a block of tokens is the dense B operand, so the
 // accumulator tile is D[weight row, token] and the epilogue writes it transposed.
 //
-// Per 128-deep K block a stage of shared memory holds
-//     A  128 rows x 64 B   compressed weights, 64-byte swizzle      (TMA)
-//     E  128 rows x 16 B   metadata, 8 nibbles per 32 K, plain rows  (TMA, no swizzle)
-//     B  block_t rows x 128 B  int8 activations, 128-byte swizzle   (TMA)
-// The MMA thread copies E into tensor memory with tcgen05.cp (128 lanes x 128 bits = the
-// metadata of two K=64 instructions) and issues two tcgen05.mma.sp per stage.  tcgen05.cp and
-// tcgen05.mma issued by one thread execute in issue order, so one 4-column metadata slot in
-// tensor memory is enough.  Roles, accumulator double-buffering and bounded waits are as in
+// Per 256-deep K block a stage of shared memory holds
+//     A  128 rows x 128 B      compressed weights, 128-byte swizzle            (TMA)
+//     E  2 x (128 rows x 16 B) metadata, 8 nibbles per 32 K, plain rows        (TMA, no swizzle)
+//     B  2 x (block_t rows x 128 B) int8 activations, 128-byte swizzle         (TMA)
+// The MMA thread copies E into tensor memory with two tcgen05.cp (128 lanes x 128 bits each =
+// the metadata of two K=64 instructions) and issues four tcgen05.mma.sp per stage.  tcgen05.cp
+// and tcgen05.mma issued by one thread execute in issue order, so one 8-column metadata slot
+// in tensor memory is enough.  Roles, accumulator double-buffering and bounded waits are as in
 // the dense kernel.
 #include "common.cuh"
 
@@ -20,9 +20,9 @@ namespace sparse {
 namespace {
 
 constexpr int kTileW = 128;          // weight rows per tile (tensor-memory lanes)
-constexpr int kBlockK = 128;         // logical K per stage
-constexpr int kABytes = kTileW * (kBlockK / 2);   // 8192
-constexpr int kEBytes = kTileW * (kBlockK / 8);   // 2048
+constexpr int kBlockK = 256;         // logical K per stage (four K=64 instructions)
+constexpr int kABytes = kTileW * (kBlockK / 2);   // 16384: 128 rows x 128 B of compressed weights
+constexpr int kEBytes = kTileW * (kBlockK / 8);   // 4096: two 128 x 16 B metadata tiles
 constexpr int kMaxStages = 8;
 constexpr int kEpiWarps = 8;
 constexpr int kEpiThreads = kEpiWarps * 32;
@@ -30,7 +30,7 @@ constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kSlabTokens = 32;                       // tokens per TMA store
 constexpr int kSlabBytes = kSlabTokens * 64;          // 32 tokens x 32 columns x 2 B
 constexpr int kSmemLimit = 227 * 1024;
-constexpr int kMaxBlockT = 240;      // 2 * 240 accumulator columns + 4 metadata columns <= 512
+constexpr int kMaxBlockT = 240;      // 2 * 240 accumulator columns + 8 metadata columns <= 512
 
 struct SparseArgs {
   const float* act_scale;
@@ -74,7 +74,8 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   uint8_t* smem = smem_raw + pad;
   const uint32_t smem_base = raw_addr + pad;
 
-  const uint32_t b_bytes = static_cast<uint32_t>(p.block_t) * 128u;
+  const uint32_t b_half = static_cast<uint32_t>(p.block_t) * 128u;   // one 128-byte-wide box of tokens
+  const uint32_t b_bytes = 2u * b_half;
   const uint32_t stage_bytes = kABytes + kEBytes + b_bytes;
   const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
   SparseCtrl* ctrl = reinterpret_cast<SparseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes +
@@ -113,71 +114,78 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   const uint32_t tmem_base = ctrl->tmem_base;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const int w0 = (tile % p.w_tiles) * kTileW;
-      const int t0 = (tile / p.w_tiles) * p.block_t;
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0) {
+    // ---------------- TMA producer (one thread) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int w0 = (tile % p.w_tiles) * kTileW;
+        const int t0 = (tile / p.w_tiles) * p.block_t;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
+          if (!ok) break;
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_base + stage * stage_bytes;
+          const uint32_t sb = sa + kABytes + kEBytes;
           mbar_arrive_expect_tx(full, stage_bytes);
           tma_load_2d(sa, &tm_w, full, kb * (kBlockK / 2), w0);
           tma_load_2d(sa + kABytes, &tm_e, full, kb * (kBlockK / 8), w0);
-          tma_load_2d(sa + kABytes + kEBytes, &tm_x, full, kb * kBlockK, t0);
+          tma_load_2d(sa + kABytes + kEBytes / 2, &tm_e, full, kb * (kBlockK / 8) + 16, w0);
+          tma_load_2d(sb, &tm_x, full, kb * kBlockK, t0);
+          tma_load_2d(sb + b_half, &tm_x, full, kb * kBlockK + 128, t0);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
-        __syncwarp();
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    const uint32_t idesc = make_idesc_i8(kTileW, static_cast<uint32_t>(p.block_t), true);
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    int it = 0;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-      const int buf = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
-                     kDevTimeoutTmemEmpty);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.block_t);
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, kDevTimeoutFull);
-        ok = __all_sync(0xffffffffu, ok);
+    // ---------------- MMA issuer (one thread) ----------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_i8(kTileW, static_cast<uint32_t>(p.block_t), true);
+      const uint64_t desc128 = make_smem_desc(0, 1024, 128);
+      const uint64_t desc_e = make_smem_desc(0, 128, 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
+                       kDevTimeoutTmemEmpty);
         if (!ok) break;
         tc_fence_after_sync();
-        if (lane == 0) {
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.block_t);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, kDevTimeoutFull);
+          if (!ok) break;
           const uint32_t sa = smem_base + stage * stage_bytes;
-          const uint64_t da = make_smem_desc(sa, 512, 64);
-          const uint64_t de = make_smem_desc(sa + kABytes, 128, 0);
-          const uint64_t db = make_smem_desc(sa + kABytes + kEBytes, 1024, 128);
-          tmem_cp_128x128b_1cta(tmem_base + e_col, de);
-          const int nk = (kb == p.num_kb - 1) ? p.last_ksteps : 2;
-          for (int k = 0; k < nk; ++k) {
-            // Per K=64 instruction: 32 compressed bytes of A (+2 address units), 64 bytes of
-            // B (+4) and two 32-bit metadata columns.
-            mma_sp_i8_1cta(d_tmem, da + 2 * k, db + 4 * k, tmem_base + e_col + 2 * k, idesc,
-                           (kb | k) != 0 ? 1u : 0u);
+          const uint32_t se = sa + kABytes;
+          const uint32_t sb = se + kEBytes;
+          const uint64_t da = desc128 | static_cast<uint64_t>((sa & 0x3FFFFu) >> 4);
+          const uint64_t db0 = desc128 | static_cast<uint64_t>((sb & 0x3FFFFu) >> 4);
+          const uint64_t db1 = desc128 | static_cast<uint64_t>(((sb + b_half) & 0x3FFFFu) >> 4);
+          // Metadata of the stage: two 128-lane x 128-bit copies = 8 columns = four K=64 steps.
+          tmem_cp_128x128b_1cta(tmem_base + e_col, desc_e | static_cast<uint64_t>((se & 0x3FFFFu) >> 4));
+          tmem_cp_128x128b_1cta(tmem_base + e_col + 4,
+                                desc_e | static_cast<uint64_t>(((se + kEBytes / 2) & 0x3FFFFu) >> 4));
+          const int nk = (kb == p.num_kb - 1) ? p.last_ksteps : 4;
+          // Per K=64 instruction: 32 compressed bytes of A (+2 address units), 64 bytes of B
+          // (+4; the second 128-byte box after two steps) and two metadata columns.
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (k < nk)
+              mma_sp_i8_1cta(d_tmem, da + 2 * k, (k < 2 ? db0 + 4 * k : db1 + 4 * (k - 2)),
+                             tmem_base + e_col + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
           tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
-        __syncwarp();
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        if (ok) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
       }
-      if (ok && lane == 0) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;                   // tensor-memory lane quarter
@@ -340,7 +348,7 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return HY3D_ERR_SHAPE;
   if (epilogue == HY3D_EPI_GEGLU && (N & 31)) return HY3D_ERR_SHAPE;
   const int64_t kblocks = (K + kBlockK - 1) / kBlockK;
-  if (meta_ld != 4 * kblocks) return HY3D_ERR_SHAPE;
+  if (meta_ld != 4 * ((K + 127) / 128)) return HY3D_ERR_SHAPE;   // rows padded to 128-deep K blocks
   if (M == 0) return HY3D_OK;
   if (!X || !w_comp || !w_meta || !out) return HY3D_ERR_ARG;
   if (out_dtype != HY3D_S32 && (!act_scale || !w_scale)) return HY3D_ERR_ARG;
@@ -364,7 +372,7 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   p.num_kb = static_cast<int>(kblocks);
   const int k_last = static_cast<int>(K - (kblocks - 1) * kBlockK);
   p.last_ksteps = (k_last + 63) / 64;
-  const int stage_bytes = kABytes + kEBytes + block_t * 128;
+  const int stage_bytes = kABytes + kEBytes + block_t * kBlockK;
   p.tma_store = (out_dtype != HY3D_S32 && epilogue != HY3D_EPI_GEGLU && block_t % kSlabTokens == 0) ? 1 : 0;
   const int fixed = static_cast<int>(sizeof(SparseCtrl)) + kEpiWarps * kSlabBytes + 1024;
   int stages = (kSmemLimit - fixed) / stage_bytes;
@@ -378,13 +386,13 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
 
   CUtensorMap tm_w, tm_e, tm_x, tm_o;
   int rc = encode_tmap_2d_u8(&tm_w, w_comp, static_cast<uint64_t>(K / 2), static_cast<uint64_t>(N),
-                             static_cast<uint64_t>(K / 2), kBlockK / 2, kTileW, 64);
+                             static_cast<uint64_t>(K / 2), 128, kTileW, 128);
   if (rc != HY3D_OK) return rc;
   rc = encode_tmap_2d_u8(&tm_e, w_meta, static_cast<uint64_t>(meta_ld * 4), static_cast<uint64_t>(N),
-                         static_cast<uint64_t>(meta_ld * 4), kBlockK / 8, kTileW, 0);
+                         static_cast<uint64_t>(meta_ld * 4), 16, kTileW, 0);
   if (rc != HY3D_OK) return rc;
   rc = encode_tmap_2d_u8(&tm_x, X, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
-                         static_cast<uint64_t>(K), kBlockK, static_cast<uint32_t>(block_t), 128);
+                         static_cast<uint64_t>(K), 128, static_cast<uint32_t>(block_t), 128);
   if (rc != HY3D_OK) return rc;
 
   if (p.tma_store) {
