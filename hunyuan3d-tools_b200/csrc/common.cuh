@@ -34,6 +34,8 @@ __device__ __forceinline__ void trace_event(int role, unsigned& idx, int ev, int
   ++idx;
 }
 #define HY3D_TRACE_DECL(name) unsigned name = (static_cast<int>(blockIdx.x) == g_trace_cta) ? 0u : 4096u
+#define HY3D_CLK() clock64()
+#define HY3D_TRACE_RAW(slot, value) do { if (static_cast<int>(blockIdx.x) == g_trace_cta) g_trace_buf[3 * 4096 + (slot)] = (value); } while (0)
 #define HY3D_TRACE_EVENT(role, idx, ev, arg) trace_event(role, idx, ev, arg)
 #ifdef HY3D_TRACE_PER_STAGE
 #define HY3D_TRACE_FINE(role, idx, ev, arg) trace_event(role, idx, ev, arg)
@@ -42,6 +44,8 @@ __device__ __forceinline__ void trace_event(int role, unsigned& idx, int ev, int
 #endif
 #else
 #define HY3D_TRACE_DECL(name) ((void)0)
+#define HY3D_CLK() 0ll
+#define HY3D_TRACE_RAW(slot, value) ((void)0)
 #define HY3D_TRACE_EVENT(role, idx, ev, arg) ((void)0)
 #define HY3D_TRACE_FINE(role, idx, ev, arg) ((void)0)
 #endif
@@ -54,6 +58,7 @@ enum DeviceError : int {
   kDevTimeoutTmemEmpty = 104,  // MMA issuer gave up waiting for a drained accumulator
   kDevTimeoutStore = 105,
   kDevTimeoutPeer = 106,       // CTA-pair handshake
+  kDevBadAlignment = 107,      // dynamic shared memory not 1024-byte aligned
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

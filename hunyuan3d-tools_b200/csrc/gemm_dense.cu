@@ -31,7 +31,8 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kBlockKBytes = 128;   // one 128-byte swizzle row of int8 = 128 K elements
 constexpr int kMaxStages = 8;
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;                       // four per 32-lane quarter of tensor memory
+constexpr int kWarpsPerQuarter = kEpiWarps / 4;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kSlabCols = 32;                       // output columns per TMA store
@@ -150,11 +151,13 @@ template <bool kBf16, int kEpi, int kG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_o, const DenseArgs p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
-  uint8_t* smem = smem_raw + pad;
-  const uint32_t smem_base = raw_addr + pad;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  const uint32_t smem_base = smem_u32(smem_raw);
+  if (smem_base & 1023u) {   // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicCAS(&g_device_status, 0, static_cast<int>(kDevBadAlignment));
+    return;
+  }
 
   const uint32_t a_bytes = kTileM * kBlockKBytes;
   // With a CTA pair (kG == 2) each CTA stages its own 128 rows of A and half of the B tile.
@@ -298,7 +301,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   } else {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;            // tensor-memory lane quarter this warp may read
-    const int half = (warp - 2) >> 2;        // which of the two warps sharing that quarter
+    const int half = (warp - 2) >> 2;        // which of the warps sharing that quarter
     const int row_in_tile = quarter * 32 + lane;
     const int et = threadIdx.x - 64;         // 0..255
     const bool geglu = kEpi == HY3D_EPI_GEGLU;
@@ -313,6 +316,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     bool ok = true;
     int it = 0;
     int cur_n0 = -1;
+    long long acc_ld = 0, acc_math = 0, acc_store = 0, acc_n = 0, acc_tile = 0, acc_wait = 0;
     const bool scaled = p.out_dtype != HY3D_S32;
     // The activation scale of the NEXT tile's row is fetched one tile ahead, and the
     // per-column scales / bias are refilled only when the tile column changes (tiles are
@@ -346,8 +350,11 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         epi_bar_sync();
         cur_n0 = n0;
       }
+      const long long w0c = HY3D_CLK();
       if (ok) ok = mbar_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag,
                              kDevTimeoutTmemFull);
+      const long long w1c = HY3D_CLK();
+      acc_wait += w1c - w0c;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) continue;   // warp-uniform; the named barriers above stay balanced
       tc_fence_after_sync();
@@ -366,50 +373,25 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const int pend = p.store_bufs - 1;
         int sb = 0;
         if (kEpi != HY3D_EPI_GEGLU) {
-          // Software pipeline over this warp's slabs: the tcgen05.ld of the next slab is in
-          // flight while the current one is converted, staged and stored.  Once the last
-          // load has landed the accumulator buffer is handed back to the MMA warp.
-          uint32_t ra[32], rb[32], packed[16];
-          int s = half;
-          __syncwarp();
-          if (s < nslab) {
-            tmem_ld_x32(t_row + s * kSlabCols, ra);
-            while (true) {
-              tmem_ld_wait();
-              const int s1 = s + 2;
-              bool last = s1 >= nslab;
-              if (!last) {
-                tmem_ld_x32(t_row + s1 * kSlabCols, rb);
-              } else {
-                tc_fence_before_sync();
-                release_acc(smem_u32(&ctrl->tmem_empty[buf]));
-                arrived = true;
-              }
-              slab_math<kBf16, kEpi>(ra, as, wsb + s * kSlabCols, bsb + s * kSlabCols, packed);
-              slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o,
-                         (n0 + s * kSlabCols) * 2, out_row, rows_in && n0 + s * kSlabCols < p.N);
-              sb = (sb + 1) % p.store_bufs;
-              if (last) break;
-              tmem_ld_wait();
-              const int s2 = s1 + 2;
-              last = s2 >= nslab;
-              if (!last) {
-                tmem_ld_x32(t_row + s2 * kSlabCols, ra);
-              } else {
-                tc_fence_before_sync();
-                release_acc(smem_u32(&ctrl->tmem_empty[buf]));
-                arrived = true;
-              }
-              slab_math<kBf16, kEpi>(rb, as, wsb + s1 * kSlabCols, bsb + s1 * kSlabCols, packed);
-              slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o,
-                         (n0 + s1 * kSlabCols) * 2, out_row, rows_in && n0 + s1 * kSlabCols < p.N);
-              sb = (sb + 1) % p.store_bufs;
-              if (last) break;
-              s = s2;
+          // Each warp takes every kWarpsPerQuarter-th slab of its quarter; once its last
+          // tcgen05.ld has landed the accumulator buffer is handed back to the MMA warp.
+          for (int s = half; s < nslab; s += kWarpsPerQuarter) {
+            uint32_t r[32], packed[16];
+            __syncwarp();
+            tmem_ld_x32(t_row + s * kSlabCols, r);
+            tmem_ld_wait();
+            if (s + kWarpsPerQuarter >= nslab) {
+              tc_fence_before_sync();
+              release_acc(smem_u32(&ctrl->tmem_empty[buf]));
+              arrived = true;
             }
+            slab_math<kBf16, kEpi>(r, as, wsb + s * kSlabCols, bsb + s * kSlabCols, packed);
+            slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o,
+                       (n0 + s * kSlabCols) * 2, out_row, rows_in && n0 + s * kSlabCols < p.N);
+            sb = (sb + 1) % p.store_bufs;
           }
         } else {
-          for (int s = half; s < nslab; s += 2) {
+          for (int s = half; s < nslab; s += kWarpsPerQuarter) {
             const int c0 = s * acc_per_slab;
             uint32_t packed[16];
             __syncwarp();
@@ -430,7 +412,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       } else if (p.tma_store) {
         // diagnostic run: epilogue work skipped
       } else if (!geglu) {
-        for (int c = 16 * half; c < p.block_n; c += 32) {
+        for (int c = 16 * half; c < p.block_n; c += 16 * kWarpsPerQuarter) {
           uint32_t r[16];
           __syncwarp();
           tmem_ld_x16(t_row + c, r);
@@ -461,7 +443,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
       } else {
         // Columns come in blocks of 32: 16 "value" columns then their 16 "gate" columns.
-        for (int c = 32 * half; c < p.block_n; c += 64) {
+        for (int c = 32 * half; c < p.block_n; c += 32 * kWarpsPerQuarter) {
           uint32_t rv[16], rg[16];
           __syncwarp();
           tmem_ld_x16(t_row + c, rv);
@@ -488,11 +470,16 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
       }
       if (threadIdx.x == 64) HY3D_TRACE_EVENT(2, tr, 5, it);
+      acc_tile += HY3D_CLK() - w1c;
       __syncwarp();
       if (!arrived) {
         tc_fence_before_sync();
         release_acc(smem_u32(&ctrl->tmem_empty[buf]));
       }
+    }
+    if (threadIdx.x == 64) {
+      HY3D_TRACE_RAW(0, acc_ld); HY3D_TRACE_RAW(1, acc_math); HY3D_TRACE_RAW(2, acc_store);
+      HY3D_TRACE_RAW(3, acc_n); HY3D_TRACE_RAW(4, acc_tile); HY3D_TRACE_RAW(5, acc_wait); HY3D_TRACE_RAW(6, it);
     }
     // Global writes of the bulk stores must be complete before the CTA retires.
     if (p.tma_store && lane == 0) tma_store_wait_all<0>();
@@ -579,14 +566,14 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   // Two staging buffers per epilogue warp unless that costs a pipeline stage below four.
   int store_bufs = 2;
   {
-    const int fixed2 = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * 2 * kSlabBytes + 1024;
+    const int fixed2 = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * 2 * kSlabBytes;
     const int fixed1 = fixed2 - kEpiWarps * kSlabBytes;
     if ((kSmemLimit - fixed2) / stage_bytes < 4 && (kSmemLimit - fixed1) / stage_bytes >= 4)
       store_bufs = 1;
     if (const char* e = getenv("HY3D_STORE_BUFS")) store_bufs = atoi(e) == 1 ? 1 : 2;
   }
   p.store_bufs = store_bufs;
-  const int fixed = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * store_bufs * kSlabBytes + 1024;
+  const int fixed = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * store_bufs * kSlabBytes;
   int stages = (kSmemLimit - fixed) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (const char* e = getenv("HY3D_STAGES")) { const int v = atoi(e); if (v >= 2 && v < stages) stages = v; }

@@ -24,7 +24,8 @@ constexpr int kBlockK = 256;         // logical K per stage (four K=64 instructi
 constexpr int kABytes = kTileW * (kBlockK / 2);   // 16384: 128 rows x 128 B of compressed weights
 constexpr int kEBytes = kTileW * (kBlockK / 8);   // 4096: two 128 x 16 B metadata tiles
 constexpr int kMaxStages = 8;
-constexpr int kEpiWarps = 8;
+constexpr int kEpiWarps = 16;                         // four per 32-lane quarter of tensor memory
+constexpr int kWarpsPerQuarter = kEpiWarps / 4;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kSlabTokens = 32;                       // tokens per TMA store
@@ -68,11 +69,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_e,
                    const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_o,
                    const SparseArgs p) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
-  uint8_t* smem = smem_raw + pad;
-  const uint32_t smem_base = raw_addr + pad;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  const uint32_t smem_base = smem_u32(smem_raw);
+  if (smem_base & 1023u) {   // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) atomicCAS(&g_device_status, 0, static_cast<int>(kDevBadAlignment));
+    return;
+  }
 
   const uint32_t b_half = static_cast<uint32_t>(p.block_t) * 128u;   // one 128-byte-wide box of tokens
   const uint32_t b_bytes = 2u * b_half;
@@ -189,7 +192,7 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   } else {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;                   // tensor-memory lane quarter
-    const int half = (warp - 2) >> 2;               // which of the two warps sharing it
+    const int half = (warp - 2) >> 2;               // which of the warps sharing it
     const int row_in_tile = quarter * 32 + lane;    // weight row within the tile
     const int et = threadIdx.x - 64;
     const bool geglu = p.epilogue == HY3D_EPI_GEGLU;
@@ -229,7 +232,7 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const int nslab = p.block_t / kSlabTokens;
         const uint32_t chunk = static_cast<uint32_t>(lane) >> 3;
         const uint32_t in_chunk = (static_cast<uint32_t>(lane) & 7u) * 2u;
-        for (int s = half; s < nslab; s += 2) {
+        for (int s = half; s < nslab; s += kWarpsPerQuarter) {
           const int c0 = s * kSlabTokens;
           uint32_t r[32];
           __syncwarp();
@@ -278,7 +281,7 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // GEGLU: weight rows come in blocks of 32 = 16 value rows then their 16 gate rows, so
         // lanes 0-15 hold values and lanes 16-31 the matching gates.
         const int64_t out_col = geglu ? ((w0 + quarter * 32) >> 1) + (lane & 15) : n;
-        for (int c = 16 * half; c < p.block_t; c += 32) {
+        for (int c = 16 * half; c < p.block_t; c += 16 * kWarpsPerQuarter) {
           uint32_t r[16];
           __syncwarp();
           tmem_ld_x16(t_row + c, r);
@@ -357,8 +360,10 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
     return HY3D_ERR_SHAPE;
 
   if (block_t == 0) {
-    block_t = 192;
-    if (M < 192) block_t = static_cast<int>((M + 15) / 16 * 16);
+    // Measured on B200: short-K layers are bound by the output write and like the wider
+    // token tile; deeper K needs a third pipeline stage, which fits with 160 tokens.
+    block_t = K <= 640 ? 192 : 160;
+    if (M < block_t) block_t = static_cast<int>((M + 31) / 32 * 32);
   }
   if (block_t < 16 || block_t > kMaxBlockT || (block_t & 15)) return HY3D_ERR_SHAPE;
 
@@ -374,7 +379,7 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   p.last_ksteps = (k_last + 63) / 64;
   const int stage_bytes = kABytes + kEBytes + block_t * kBlockK;
   p.tma_store = (out_dtype != HY3D_S32 && epilogue != HY3D_EPI_GEGLU && block_t % kSlabTokens == 0) ? 1 : 0;
-  const int fixed = static_cast<int>(sizeof(SparseCtrl)) + kEpiWarps * kSlabBytes + 1024;
+  const int fixed = static_cast<int>(sizeof(SparseCtrl)) + kEpiWarps * kSlabBytes;
   int stages = (kSmemLimit - fixed) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 2) return HY3D_ERR_SHAPE;
