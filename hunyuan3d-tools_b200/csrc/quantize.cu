@@ -53,7 +53,7 @@ __device__ __forceinline__ uint32_t quant_one(float x, float scale, float inv) {
 // G threads cooperate on one row (G a power of two, 1..256); each holds up to kMaxV
 // 16-byte vectors.  A block of 256 threads covers 256/G rows.
 template <bool kBf16, int kMaxV>
-__global__ void __launch_bounds__(kQuantThreads)
+__global__ void __launch_bounds__(kQuantThreads, kMaxV <= 5 ? 4 : 3)
 quantize_rows_kernel(const uint16_t* __restrict__ x, int64_t ldx, int8_t* __restrict__ q,
                      float* __restrict__ scale_out, int64_t M, int K, int G) {
   __shared__ float s_part[kQuantThreads / 32];
