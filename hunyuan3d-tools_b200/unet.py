@@ -1,0 +1,268 @@
+"""A self-contained SD2.1-architecture UNet with multiview attention, used as the caller of
+the INT8 linear path in the denoise benchmarks.
+
+The reference's model-level tools build ``diffusers.UNet2DConditionModel`` with the
+Hunyuan3D-2.1 paint configuration (``tools/test_sparse_unet.py:69-90``,
+``tools/test_mixed_vs_all.py:15-24``): channels 320/640/1280/1280, two residual blocks per
+level, cross-attention in the first three down levels and the last three up levels, attention
+head counts 5/10/20/20 (head_dim 64), 1024-wide conditioning of 77 tokens, linear projections
+in the spatial transformers.  ``diffusers`` is not a dependency here, so the same architecture
+is written out below from that configuration; weights are random (there are no checkpoints
+offline).  On top of it every transformer block gets one multiview self-attention over the
+concatenated tokens of all views of a sample, as the texture pipeline's UNet has.
+
+Every ``nn.Linear`` inside is a plain ``nn.Linear`` until
+``quantize_utils.quantize_model_{tensorcore,sparse,mixed}`` swaps it, exactly how the
+reference treats the upstream UNet (``texture.py:116-131``).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+def timestep_embedding(t: torch.Tensor, dim: int) -> torch.Tensor:
+    """Sinusoidal embedding (flip_sin_to_cos, freq_shift 0 as in SD2.1)."""
+    half = dim // 2
+    freqs = torch.exp(-math.log(10000.0) * torch.arange(half, device=t.device, dtype=torch.float32) / half)
+    args = t.float()[:, None] * freqs[None, :]
+    return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
+
+
+class ResnetBlock(nn.Module):
+    def __init__(self, cin: int, cout: int, temb_dim: int):
+        super().__init__()
+        self.norm1 = nn.GroupNorm(32, cin, eps=1e-5)
+        self.conv1 = nn.Conv2d(cin, cout, 3, padding=1)
+        self.time_emb_proj = nn.Linear(temb_dim, cout)
+        self.norm2 = nn.GroupNorm(32, cout, eps=1e-5)
+        self.conv2 = nn.Conv2d(cout, cout, 3, padding=1)
+        self.conv_shortcut = nn.Conv2d(cin, cout, 1) if cin != cout else None
+
+    def forward(self, x, temb):
+        h = self.conv1(F.silu(self.norm1(x)))
+        h = h + self.time_emb_proj(F.silu(temb))[:, :, None, None]
+        h = self.conv2(F.silu(self.norm2(h)))
+        if self.conv_shortcut is not None:
+            x = self.conv_shortcut(x)
+        return x + h
+
+
+class Attention(nn.Module):
+    """Multi-head attention with separate q/k/v projections (no bias) and an output
+    projection, the layout of diffusers' ``Attention``."""
+
+    def __init__(self, dim: int, heads: int, context_dim: int | None = None):
+        super().__init__()
+        self.heads = heads
+        ctx = context_dim or dim
+        self.to_q = nn.Linear(dim, dim, bias=False)
+        self.to_k = nn.Linear(ctx, dim, bias=False)
+        self.to_v = nn.Linear(ctx, dim, bias=False)
+        self.to_out = nn.Linear(dim, dim)
+
+    def forward(self, x, context=None):
+        context = x if context is None else context
+        b, n, c = x.shape
+        q = self.to_q(x).view(b, n, self.heads, c // self.heads).transpose(1, 2)
+        k = self.to_k(context).view(b, context.shape[1], self.heads, c // self.heads).transpose(1, 2)
+        v = self.to_v(context).view(b, context.shape[1], self.heads, c // self.heads).transpose(1, 2)
+        o = F.scaled_dot_product_attention(q, k, v)
+        return self.to_out(o.transpose(1, 2).reshape(b, n, c))
+
+
+class GEGLUFeedForward(nn.Module):
+    """Linear(C, 8C) -> value * gelu(gate) -> Linear(4C, C).  When the up-projection has been
+    converted to an ``Int8Linear`` with the fused GEGLU epilogue it already returns 4C columns."""
+
+    def __init__(self, dim: int):
+        super().__init__()
+        self.proj = nn.Linear(dim, dim * 8)
+        self.out = nn.Linear(dim * 4, dim)
+
+    def forward(self, x):
+        h = self.proj(x)
+        if h.shape[-1] == self.out.in_features * 2:
+            value, gate = h.chunk(2, dim=-1)
+            h = value * F.gelu(gate)
+        return self.out(h)
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, dim: int, heads: int, context_dim: int, num_views: int):
+        super().__init__()
+        self.num_views = num_views
+        self.norm1 = nn.LayerNorm(dim)
+        self.attn1 = Attention(dim, heads)
+        self.norm_mv = nn.LayerNorm(dim)
+        self.attn_mv = Attention(dim, heads)          # multiview: all views of a sample at once
+        self.norm2 = nn.LayerNorm(dim)
+        self.attn2 = Attention(dim, heads, context_dim)
+        self.norm3 = nn.LayerNorm(dim)
+        self.ff = GEGLUFeedForward(dim)
+
+    def forward(self, x, context):
+        x = x + self.attn1(self.norm1(x))
+        if self.num_views > 1:
+            b, n, c = x.shape
+            xv = self.norm_mv(x).view(b // self.num_views, self.num_views * n, c)
+            x = x + self.attn_mv(xv).view(b, n, c)
+        x = x + self.attn2(self.norm2(x), context)
+        return x + self.ff(self.norm3(x))
+
+
+class SpatialTransformer(nn.Module):
+    def __init__(self, dim: int, heads: int, context_dim: int, num_views: int):
+        super().__init__()
+        self.norm = nn.GroupNorm(32, dim, eps=1e-6)
+        self.proj_in = nn.Linear(dim, dim)
+        self.block = TransformerBlock(dim, heads, context_dim, num_views)
+        self.proj_out = nn.Linear(dim, dim)
+
+    def forward(self, x, context):
+        b, c, h, w = x.shape
+        y = self.norm(x).permute(0, 2, 3, 1).reshape(b, h * w, c)
+        y = self.proj_out(self.block(self.proj_in(y), context))
+        return x + y.view(b, h, w, c).permute(0, 3, 1, 2)
+
+
+class Downsample(nn.Module):
+    def __init__(self, c):
+        super().__init__()
+        self.conv = nn.Conv2d(c, c, 3, stride=2, padding=1)
+
+    def forward(self, x):
+        return self.conv(x)
+
+
+class Upsample(nn.Module):
+    def __init__(self, c):
+        super().__init__()
+        self.conv = nn.Conv2d(c, c, 3, padding=1)
+
+    def forward(self, x):
+        return self.conv(F.interpolate(x, scale_factor=2.0, mode="nearest"))
+
+
+class UNetSD21MV(nn.Module):
+    """UNet2DConditionModel of the Hunyuan3D-2.1 paint configuration + multiview attention."""
+
+    def __init__(self, in_channels=4, out_channels=4, block_out_channels=(320, 640, 1280, 1280),
+                 layers_per_block=2, attention_heads=(5, 10, 20, 20), cross_attention_dim=1024,
+                 num_views=6, attn_levels=(True, True, True, False)):
+        super().__init__()
+        ch = list(block_out_channels)
+        self.num_views = num_views
+        temb = ch[0] * 4
+        self.time_proj_dim = ch[0]
+        self.time_embedding = nn.Sequential(nn.Linear(ch[0], temb), nn.SiLU(), nn.Linear(temb, temb))
+        self.conv_in = nn.Conv2d(in_channels, ch[0], 3, padding=1)
+
+        self.down = nn.ModuleList()
+        skip_channels = [ch[0]]
+        cin = ch[0]
+        for lvl, cout in enumerate(ch):
+            for _ in range(layers_per_block):
+                layer = nn.ModuleDict({"res": ResnetBlock(cin, cout, temb)})
+                if attn_levels[lvl]:
+                    layer["attn"] = SpatialTransformer(cout, attention_heads[lvl], cross_attention_dim, num_views)
+                self.down.append(layer)
+                cin = cout
+                skip_channels.append(cout)
+            if lvl != len(ch) - 1:
+                self.down.append(nn.ModuleDict({"down": Downsample(cout)}))
+                skip_channels.append(cout)
+
+        self.mid_res1 = ResnetBlock(ch[-1], ch[-1], temb)
+        self.mid_attn = SpatialTransformer(ch[-1], attention_heads[-1], cross_attention_dim, num_views)
+        self.mid_res2 = ResnetBlock(ch[-1], ch[-1], temb)
+
+        self.up = nn.ModuleList()
+        rev = list(reversed(ch))
+        rev_attn = list(reversed(attn_levels))
+        rev_heads = list(reversed(attention_heads))
+        for lvl, cout in enumerate(rev):
+            for i in range(layers_per_block + 1):
+                skip = skip_channels.pop()
+                layer = nn.ModuleDict({"res": ResnetBlock(cin + skip, cout, temb)})
+                if rev_attn[lvl]:
+                    layer["attn"] = SpatialTransformer(cout, rev_heads[lvl], cross_attention_dim, num_views)
+                if i == layers_per_block and lvl != len(rev) - 1:
+                    layer["up"] = Upsample(cout)
+                self.up.append(layer)
+                cin = cout
+
+        self.norm_out = nn.GroupNorm(32, ch[0], eps=1e-5)
+        self.conv_out = nn.Conv2d(ch[0], out_channels, 3, padding=1)
+
+    def forward(self, x, t, context):
+        """x: (B*views, 4, H, W); t: (B*views,) or scalar tensor; context: (B*views, 77, 1024)."""
+        if t.dim() == 0:
+            t = t.expand(x.shape[0])
+        temb = self.time_embedding(timestep_embedding(t, self.time_proj_dim).to(x.dtype))
+        h = self.conv_in(x)
+        skips = [h]
+        for layer in self.down:
+            if "down" in layer:
+                h = layer["down"](h)
+            else:
+                h = layer["res"](h, temb)
+                if "attn" in layer:
+                    h = layer["attn"](h, context)
+            skips.append(h)
+        h = self.mid_res2(self.mid_attn(self.mid_res1(h, temb), context), temb)
+        for layer in self.up:
+            h = layer["res"](torch.cat([h, skips.pop()], dim=1), temb)
+            if "attn" in layer:
+                h = layer["attn"](h, context)
+            if "up" in layer:
+                h = layer["up"](h)
+        return self.conv_out(F.silu(self.norm_out(h)))
+
+
+def fuse_geglu_layers(model: nn.Module) -> int:
+    """Switches every dense ``Int8Linear`` GEGLU up-projection to the fused
+    ``value * gelu(gate)`` epilogue (rows interleaved offline).  Returns the number fused."""
+    from .quantize_utils import Int8Linear
+    n = 0
+    for m in model.modules():
+        if isinstance(m, GEGLUFeedForward) and isinstance(m.proj, Int8Linear) and m.proj.mode == "tc" \
+                and m.proj.epilogue == "linear":
+            m.proj.interleave_geglu_rows()
+            n += 1
+    return n
+
+
+# -----------------------------------------------------------------------------------------
+# Denoising loop (deterministic DDIM, classifier-free guidance)
+# -----------------------------------------------------------------------------------------
+def ddim_alphas(num_train_steps=1000, beta_start=0.00085, beta_end=0.012):
+    betas = torch.linspace(beta_start ** 0.5, beta_end ** 0.5, num_train_steps, dtype=torch.float64) ** 2
+    return torch.cumprod(1.0 - betas, dim=0)
+
+
+@torch.no_grad()
+def denoise(unet: UNetSD21MV, latents: torch.Tensor, cond: torch.Tensor, uncond: torch.Tensor,
+            steps: int = 10, guidance: float = 3.0, step_fn=None) -> torch.Tensor:
+    """latents: (views, 4, H, W) of ONE mesh; cond / uncond: (views, 77, 1024).  Each step runs
+    the UNet once on the 2 x views batch [uncond | cond] and applies a deterministic DDIM update
+    with guidance scale ``guidance`` (3.0 is the texture pipeline's value).  ``step_fn`` lets a
+    caller substitute a CUDA-graph replay for the eager UNet call."""
+    acp = ddim_alphas().to(latents.device)
+    ts = torch.linspace(999, 0, steps + 1).long()[:-1]
+    context = torch.cat([uncond, cond], dim=0)
+    x = latents
+    for i, t in enumerate(ts):
+        t_dev = torch.full((2 * x.shape[0],), int(t), device=x.device, dtype=torch.long)
+        inp = torch.cat([x, x], dim=0)
+        eps = step_fn(inp, t_dev, context) if step_fn is not None else unet(inp, t_dev, context)
+        eps_u, eps_c = eps.float().chunk(2, dim=0)
+        eps = eps_u + guidance * (eps_c - eps_u)
+        a_t = acp[int(t)]
+        a_prev = acp[int(ts[i + 1])] if i + 1 < len(ts) else torch.tensor(1.0, dtype=torch.float64, device=x.device)
+        x0 = (x.float() - (1 - a_t).sqrt().float() * eps) / a_t.sqrt().float()
+        x = (a_prev.sqrt().float() * x0 + (1 - a_prev).sqrt().float() * eps).to(latents.dtype)
+    return x

@@ -1,0 +1,125 @@
+"""GPU: the SD2.1-architecture UNet with INT8 linears against the same UNet whose linears run
+the oracle's W8A8 arithmetic in plain torch ops (same int8 weights, same activation
+quantiser, exact integer matmul, same epilogue formula)."""
+import importlib
+
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import oracle as O
+from conftest import PKG_NAME
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+class OracleInt8Linear(nn.Module):
+    """Torch-op restatement of one Int8Linear (dense or 2:4 sparse) for parity checks."""
+
+    def __init__(self, layer):
+        super().__init__()
+        self.in_features, self.out_features = layer.in_features, layer.out_features
+        if layer.mode == "sparse":
+            K = layer.in_features
+            nib = O.unpack_metadata(layer.weight_sparse_meta.cpu(), K)
+            w = O.expand_24(layer.weight_sparse_comp.cpu(), nib)
+        else:
+            w = layer.weight_int8_nk.cpu()
+        self.w = w.to(DEV).double()
+        self.scale = layer.weight_scale.float()
+        self.bias = None if layer.bias is None else layer.bias.float()
+        self.epilogue = layer.epilogue
+
+    def forward(self, x):
+        shape = x.shape
+        xf = x.reshape(-1, shape[-1]).float()
+        amax = xf.abs().amax(dim=1)
+        s = torch.clamp(amax, min=1e-8) / torch.full_like(amax, 127.0)
+        q = (xf / s[:, None]).round().clamp(-128, 127)
+        acc = q.double() @ self.w.t()                       # exact: |acc| < 2^53
+        y = acc.float() * (s[:, None] * self.scale[None, :])
+        if self.bias is not None:
+            y = y + self.bias[None, :]
+        if self.epilogue == "geglu":
+            M, N = y.shape
+            y = y.view(M, N // 32, 2, 16)
+            y = (y[:, :, 0] * torch.nn.functional.gelu(y[:, :, 1])).reshape(M, N // 2)
+        return y.to(x.dtype).reshape(*shape[:-1], y.shape[-1])
+
+
+def _twin(unet, qu):
+    import copy
+    twin = copy.deepcopy(unet)
+
+    def swap(mod):
+        for name, child in list(mod.named_children()):
+            if isinstance(child, qu.Int8Linear):
+                setattr(mod, name, OracleInt8Linear(child))
+            else:
+                swap(child)
+    swap(twin)
+    return twin
+
+
+SMALL = dict(block_out_channels=(128, 256), attention_heads=(2, 4), cross_attention_dim=128,
+             num_views=2, attn_levels=(True, True))
+
+
+def test_reduced_unet_ten_steps_matches_oracle_linears():
+    qu = importlib.import_module(PKG_NAME + ".quantize_utils")
+    mm = importlib.import_module(PKG_NAME + ".multimesh")
+    un = importlib.import_module(PKG_NAME + ".unet")
+    unet, stats = mm.build_texture_unet(DEV, torch.bfloat16, "mixed", seed=0, **SMALL)
+    assert stats["sparse_layers"] > 0 and stats["dense_layers"] > 0 and stats["geglu_fused"] > 0
+    twin = _twin(unet, qu)
+    g = torch.Generator().manual_seed(0)
+    lat = torch.randn(2, 4, 16, 16, generator=g).bfloat16().to(DEV)
+    cond = torch.randn(2, 7, 128, generator=g).bfloat16().to(DEV)
+    uncond = torch.zeros_like(cond)
+    # one forward: same inputs, layer-by-layer identical accumulators -> bf16 rounding noise only
+    x = torch.cat([lat, lat]); ctx = torch.cat([uncond, cond]); t = torch.full((4,), 500, device=DEV)
+    with torch.no_grad():
+        y, y_ref = unet(x, t, ctx), twin(x, t, ctx)
+    assert not torch.isnan(y).any()
+    assert O.rel_l2(y, y_ref) < 2e-2
+    a = un.denoise(unet, lat, cond, uncond, steps=10, guidance=3.0)
+    b = un.denoise(twin, lat, cond, uncond, steps=10, guidance=3.0)
+    assert not torch.isnan(a).any()
+    assert O.rel_l2(a, b) < 2e-2          # the stated gate on latents after 10 steps
+
+
+def test_graphed_step_equals_eager():
+    mm = importlib.import_module(PKG_NAME + ".multimesh")
+    un = importlib.import_module(PKG_NAME + ".unet")
+    unet, _ = mm.build_texture_unet(DEV, torch.bfloat16, "mixed", seed=1, **SMALL)
+    lat, cond, uncond = mm.mesh_inputs(5, views=2, size=16, ctx_tokens=7, ctx_dim=128, device=DEV)
+    eager = un.denoise(unet, lat, cond, uncond, steps=3)
+    step = mm.GraphedStep(unet, 4, 16, 7, 128, torch.bfloat16, DEV)
+    graphed = un.denoise(unet, lat, cond, uncond, steps=3, step_fn=step)
+    assert torch.equal(eager, graphed)
+
+
+def test_full_size_unet_step_runs_and_layer_census():
+    """Full paint configuration, 2 x 6 views of 64 x 64 latents: layer counts follow the
+    reference's table (tools/profile_unet_shapes.py:32-51 plus four multiview projections per
+    transformer block); one step gives finite outputs and agrees with the unquantised model."""
+    qu = importlib.import_module(PKG_NAME + ".quantize_utils")
+    mm = importlib.import_module(PKG_NAME + ".multimesh")
+    unet, stats = mm.build_texture_unet(DEV, torch.bfloat16, "none", seed=0)
+    from collections import Counter
+    census = Counter((m.in_features, m.out_features) for m in unet.modules() if isinstance(m, nn.Linear))
+    assert census[(320, 320)] == 60 and census[(640, 640)] == 60 and census[(1280, 1280)] == 85
+    assert census[(320, 2560)] == 5 and census[(640, 5120)] == 5 and census[(1280, 10240)] == 6
+    assert census[(1024, 320)] == 10 and census[(1024, 640)] == 10 and census[(1024, 1280)] == 12
+    lat, cond, uncond = mm.mesh_inputs(0, device=DEV)
+    x = torch.cat([lat, lat]); ctx = torch.cat([uncond, cond]); t = torch.full((12,), 500, device=DEV)
+    with torch.no_grad():
+        ref = unet(x, t, ctx)
+    stats = qu.quantize_model_mixed(unet, verbose=False)
+    assert stats["num_replaced"] == 280
+    with torch.no_grad():
+        y = unet(x, t, ctx)
+    assert y.shape == (12, 4, 64, 64) and not torch.isnan(y).any()
+    # W8A8 (+2:4 pruning of K >= 640 layers of a random-init net) against bf16: same ballpark
+    assert O.rel_l2(y, ref) < 0.5
