@@ -2,7 +2,7 @@
 """Benchmark of the W8A8 linear hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload dense_sweep|sparse_sweep]
+                    [--workload dense_sweep|sparse_sweep|unet|multimesh] [--quant mixed|dense|sparse|none]
 
 One "step" is one pass over the twelve SD2.1-style texture-UNet linear shapes (M = 2 x 6 views x
 tokens per level: 49152 / 12288 / 3072 rows, plus the three cross-attention K/V shapes at
@@ -396,13 +396,113 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------
+# UNet denoise (BASELINE configs[3]) and multi-mesh batch (configs[4])
+# ---------------------------------------------------------------------------------------
+def run_unet(args):
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    mm = importlib.import_module("hunyuan3d-tools_b200.multimesh")
+    un = importlib.import_module("hunyuan3d-tools_b200.unet")
+    unet, stats = mm.build_texture_unet(dev, torch.bfloat16, args.quant, seed=0)
+    step = mm.GraphedStep(unet, 12, 64, 77, 1024, torch.bfloat16, dev)
+
+    def sync_max(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if args.workload == "unet":
+        for _ in range(args.warmup):
+            step.graph.replay()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler:
+            sampler.start()
+        e0.record()
+        for _ in range(args.steps):
+            step.graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.stop()
+        ms_step = sync_max(e0.elapsed_time(e1) / args.steps)
+        # end to end: host latents / context in, 10-step loop, host latents out
+        lat, cond, uncond = mm.mesh_inputs(1000 + rank)
+        lat, cond, uncond = lat.pin_memory(), cond.pin_memory(), uncond.pin_memory()
+        host_out = torch.empty_like(lat).pin_memory()
+        torch.cuda.synchronize()
+        e0.record()
+        out = un.denoise(unet, lat.to(dev, non_blocking=True), cond.to(dev, non_blocking=True),
+                         uncond.to(dev, non_blocking=True), steps=10, step_fn=step)
+        host_out.copy_(out, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        e2e_ms = sync_max(e0.elapsed_time(e1) / 10)
+        if rank == 0:
+            print(json.dumps({
+                "metric": "UNet denoise ms/step (6 views)", "value": round(ms_step, 3), "unit": "ms",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 3),
+                "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 + W8A8 linears",
+                "data": "synthetic",
+                "config": {"workload": "one denoise step of the random-init SD2.1-architecture UNet, 2 (CFG) x 6 views "
+                                       "x 64x64x4 latents, multiview attention (BASELINE configs[3])",
+                           "quant": args.quant, "layers": stats,
+                           "timing": "CUDA-graph replay of the 12-sample forward, one mesh per rank"},
+                "e2e": {"value": round(e2e_ms, 3), "unit": "ms", "h2d_bytes_per_step": int((lat.numel() + 2 * cond.numel()) * 2 / 10),
+                        "d2h_bytes_per_step": int(lat.numel() * 2 / 10)},
+                "meshes_per_s": round(world / (10 * ms_step * 1e-3), 2),
+                "clocks": sampler.summary(len(sampler.samples)) if sampler else None,
+            }), flush=True)
+    else:   # multimesh: 32 meshes sharded over the ranks, latents gathered on rank 0
+        seeds = list(range(32))
+        mine = mm.partition(seeds, rank, world)
+        mm.denoise_meshes(unet, mine[:1], device=dev)           # warm-up
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        local, _ = mm.denoise_meshes(unet, mine, device=dev)
+        results, missing = mm.gather_results(local, seeds, (6, 4, 64, 64), torch.bfloat16, dev, dst=0)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        dt = sync_max(dt * 1e3) * 1e-3
+        if rank == 0:
+            print(json.dumps({
+                "metric": "multi-mesh texture batch, meshes/s", "value": round(32 / dt, 3), "unit": "meshes/s",
+                "n_gpus": world, "steps": 10, "warmup": 1, "ms_per_step": round(dt * 1e3 / (10 * len(mine)), 3),
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 + W8A8 linears",
+                "data": "synthetic",
+                "config": {"workload": "32 meshes x 10 INT8 denoise steps, seeds 0..31 sharded round-robin, "
+                                       "bf16 latents gathered on rank 0 (BASELINE configs[4])", "quant": args.quant},
+                "missing": missing, "collected": len(results),
+            }), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense_sweep", choices=["dense_sweep", "sparse_sweep"])
+    ap.add_argument("--workload", default="dense_sweep", choices=["dense_sweep", "sparse_sweep", "unet", "multimesh"])
+    ap.add_argument("--quant", default="mixed", choices=["mixed", "dense", "sparse", "none"])
     ap.add_argument("--cpu-frac", type=float, default=1.0, help="row fraction of each shape timed on the CPU")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -410,6 +510,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in ("unet", "multimesh"):
+        run_unet(args)
     else:
         run_ours(args)
 
