@@ -47,7 +47,7 @@ struct DenseArgs {
   int ws_dtype, bias_dtype, out_dtype, epilogue;
   int M, N, K;
   int block_n, stages, acc_cols, tma_store, store_bufs;
-  int m_tiles, n_tiles, num_kb, last_ksteps;
+  int m_tiles, n_tiles, num_kb, last_ksteps, n_fastest;
   int debug;   // diagnostic switches (HY3D_DEBUG): 1 no TMA loads, 2 no epilogue work, 4 no MMA
 };
 
@@ -173,6 +173,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const int total_tiles = p.m_tiles * p.n_tiles;     // m_tiles counts 128*kG-row units
   const uint32_t cta_rank = kG == 2 ? cluster_cta_rank() : 0u;
   const bool leader = cta_rank == 0;                 // issues the MMAs for the pair
+  // Tile order: M-fastest (CTAs running together share a B tile) or N-fastest (they share an A
+  // tile, so a large A is fetched from HBM once); see the host-side choice.
+  auto tile_m = [&](int t) { return p.n_fastest ? t / p.n_tiles : t % p.m_tiles; };
+  auto tile_n = [&](int t) { return p.n_fastest ? t % p.n_tiles : t / p.m_tiles; };
   const int first_tile = static_cast<int>(blockIdx.x) / kG;
   const int tile_step = static_cast<int>(gridDim.x) / kG;
   const int row_off = static_cast<int>(cta_rank) * kTileM;
@@ -216,8 +220,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
-        const int m0 = (tile % p.m_tiles) * (kTileM * kG) + row_off;
-        const int n0 = (tile / p.m_tiles) * p.block_n + col_off;
+        const int m0 = tile_m(tile) * (kTileM * kG) + row_off;
+        const int n0 = tile_n(tile) * p.block_n + col_off;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
           if (!ok) break;
@@ -323,20 +327,20 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // walked M-fastest, so consecutive tiles of a CTA mostly share their columns).
     float as_next = 0.0f;
     if (scaled && first_tile < total_tiles) {
-      const int m_first = (first_tile % p.m_tiles) * (kTileM * kG) + row_off + row_in_tile;
+      const int m_first = tile_m(first_tile) * (kTileM * kG) + row_off + row_in_tile;
       if (m_first < p.M) as_next = p.act_scale[m_first];
     }
     for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (tile % p.m_tiles) * (kTileM * kG) + row_off;
-      const int n0 = (tile / p.m_tiles) * p.block_n;
+      const int m0 = tile_m(tile) * (kTileM * kG) + row_off;
+      const int n0 = tile_n(tile) * p.block_n;
       const float as = as_next;
       {
         const int nt = tile + tile_step;
         as_next = 0.0f;
         if (scaled && nt < total_tiles) {
-          const int mn = (nt % p.m_tiles) * (kTileM * kG) + row_off + row_in_tile;
+          const int mn = tile_m(nt) * (kTileM * kG) + row_off + row_in_tile;
           if (mn < p.M) as_next = p.act_scale[mn];
         }
       }
@@ -625,7 +629,22 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.m_tiles * p.n_tiles;
   const int max_clusters = sms / group;
-  const int grid = group * (total_tiles < max_clusters ? total_tiles : max_clusters);
+  int clusters = total_tiles < max_clusters ? total_tiles : max_clusters;
+  // A large activation matrix (it would not survive in L2 between passes over the tile
+  // columns) is walked N-fastest so that every A tile is fetched once while B, which is
+  // small, stays L2-resident.  Rounding the grid down to a multiple of the column count keeps
+  // one tile column per CTA, so its per-column scales are staged once.
+  p.n_fastest = 0;
+  if (static_cast<int64_t>(M) * K > (24ll << 20) && p.n_tiles > 1) {
+    p.n_fastest = 1;
+    if (p.n_tiles <= clusters / 4) clusters -= clusters % p.n_tiles;
+  }
+  if (const char* e = getenv("HY3D_ORDER")) {
+    p.n_fastest = atoi(e) ? 1 : 0;
+    clusters = total_tiles < max_clusters ? total_tiles : max_clusters;
+    if (p.n_fastest && p.n_tiles <= clusters / 4) clusters -= clusters % p.n_tiles;
+  }
+  const int grid = group * clusters;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
   cfg.blockDim = dim3(kThreads);
