@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/hy3d_int8.h"
 
@@ -79,6 +80,18 @@ __device__ __forceinline__ bool elect_one() {
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(pred));
   return pred != 0;
+}
+
+// ------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the programmatic-serialisation
+// attribute may start while its predecessor in the stream is still running; everything
+// before pdl_wait() (barrier set-up, tensor-memory allocation, descriptor prefetch) overlaps
+// with the predecessor's tail, everything after it sees the predecessor's memory complete.
+// Without the launch attribute both are no-ops.
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // ------------------------------------------------------------------------------------
@@ -398,6 +411,24 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, int out_dtype) {
   }
   __half2 v = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+
+// Host side: launch attribute that lets a kernel start before its stream predecessor ends
+// (HY3D_PDL=0 in the environment turns it off).
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("HY3D_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+inline cudaLaunchAttribute pdl_attribute() {
+  cudaLaunchAttribute a = {};
+  a.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  a.val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  return a;
 }
 
 }  // namespace hy3d

@@ -212,6 +212,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
   HY3D_TRACE_DECL(tr);
+  // Set-up done: let the next kernel in the stream begin its own, then wait until the
+  // previous one (which produced A and the scales) has completed.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ---------------- TMA producer (one thread) ----------------
@@ -650,13 +654,14 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  attr[1] = pdl_attribute();
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(group);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   if (cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_o, p) != cudaSuccess) {
     cudaGetLastError();
     return HY3D_ERR_CUDA;

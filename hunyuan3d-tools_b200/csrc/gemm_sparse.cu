@@ -115,6 +115,8 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ---------------- TMA producer (one thread) ----------------
@@ -422,8 +424,19 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.w_tiles * p.t_tiles;
   const int grid = total_tiles < sms ? total_tiles : sms;
-  gemm_sparse_kernel<<<grid, kThreads, smem_bytes, stream>>>(tm_w, tm_e, tm_x, tm_o, p);
-  return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1] = {pdl_attribute()};
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm_sparse_kernel, tm_w, tm_e, tm_x, tm_o, p) != cudaSuccess) {
+    cudaGetLastError();
+    return HY3D_ERR_CUDA;
+  }
+  return HY3D_OK;
 }
 
 }  // namespace sparse

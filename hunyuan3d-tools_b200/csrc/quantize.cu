@@ -71,6 +71,8 @@ __global__ void __launch_bounds__(kQuantThreads, kMaxV <= 5 ? 4 : 3)
 quantize_rows_kernel(const uint16_t* __restrict__ x, int64_t ldx, int8_t* __restrict__ q,
                      float* __restrict__ scale_out, int64_t M, int K, int G) {
   __shared__ float s_part[kQuantThreads / 32];
+  pdl_launch_dependents();
+  pdl_wait();   // x comes from the previous kernel in the stream
   const int tid = threadIdx.x;
   const int rows_per_block = kQuantThreads / G;
   const int sub = tid % G;  // position within the row group
@@ -146,9 +148,17 @@ int launch_quantize(const void* x, int64_t M, int64_t K, int64_t ldx, int8_t* q,
   if (blocks > 0x7FFFFFFF) return HY3D_ERR_SHAPE;
   const uint16_t* xp = reinterpret_cast<const uint16_t*>(x);
   dim3 grid(static_cast<unsigned>(blocks));
-#define HY3D_LAUNCH_Q(V)                                                                   \
-  quantize_rows_kernel<kBf16, V><<<grid, kQuantThreads, 0, stream>>>(xp, ldx, q, scale, M, \
-                                                                     static_cast<int>(K), G)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kQuantThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1] = {pdl_attribute()};
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t err = cudaSuccess;
+  const int Ki = static_cast<int>(K);
+#define HY3D_LAUNCH_Q(V) \
+  err = cudaLaunchKernelEx(&cfg, quantize_rows_kernel<kBf16, V>, xp, ldx, q, scale, M, Ki, G)
   switch (maxv) {
     case 1: HY3D_LAUNCH_Q(1); break;
     case 2: HY3D_LAUNCH_Q(2); break;
@@ -160,7 +170,11 @@ int launch_quantize(const void* x, int64_t M, int64_t K, int64_t ldx, int8_t* q,
     default: HY3D_LAUNCH_Q(8); break;
   }
 #undef HY3D_LAUNCH_Q
-  return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return HY3D_ERR_CUDA;
+  }
+  return HY3D_OK;
 }
 
 // out[m,n] = acc[m,n] * (act_scale[m] * w_scale[n]) + bias[n]; 8 columns per thread.
