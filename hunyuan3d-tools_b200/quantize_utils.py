@@ -177,6 +177,33 @@ class Int8Linear(nn.Module):
         layer.mode = "sparse"
         return layer.to(device)
 
+    # -- checkpointing -----------------------------------------------------------------
+    # The reference registers the sparse buffers as None, so a freshly constructed layer
+    # cannot load a sparse checkpoint (quantize_utils.py:190-192).  Here the mode, epilogue
+    # and buffer shapes travel with the state dict, so a pruned + packed model reloads
+    # without re-pruning.
+    def get_extra_state(self):
+        return {"mode": self.mode, "epilogue": self.epilogue, "layout": "hy3d-int8-v1"}
+
+    def set_extra_state(self, state):
+        self.mode = state.get("mode", "tc")
+        self.epilogue = state.get("epilogue", "linear")
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys,
+                              unexpected_keys, error_msgs):
+        # Re-shape this layer's buffers to whatever the checkpoint holds (dense weights may be
+        # empty, sparse buffers may be present) before the generic copy runs.
+        for name in ("weight_int8_nk", "weight_scale", "weight_sparse_comp", "weight_sparse_meta", "bias"):
+            key = prefix + name
+            if key in state_dict:
+                src = state_dict[key]
+                cur = getattr(self, name, None)
+                if cur is None or cur.shape != src.shape or cur.dtype != src.dtype:
+                    device = self.weight_scale.device
+                    self.register_buffer(name, torch.empty(src.shape, dtype=src.dtype, device=device))
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys,
+                                      unexpected_keys, error_msgs)
+
     def interleave_geglu_rows(self) -> "Int8Linear":
         """Re-orders a GEGLU up-projection ([value(H) | gate(H)] output rows) into blocks of
         16 value rows followed by their 16 gate rows and switches the layer to the fused

@@ -156,3 +156,20 @@ def test_kernels_run_on_the_current_stream_and_capture(qu):
     g.replay()
     torch.cuda.synchronize()
     assert torch.equal(y, eager)
+
+
+def test_sparse_state_dict_roundtrip(qu):
+    """A pruned + packed layer reloads into a fresh module without re-pruning (the reference
+    cannot: its sparse buffers are registered as None)."""
+    torch.manual_seed(7)
+    lin = nn.Linear(1280, 640).to(DEV).bfloat16()
+    a = qu.Int8Linear.from_linear_sparse(lin)
+    sd = {k: v.cpu() if torch.is_tensor(v) else v for k, v in a.state_dict().items()}
+    b = qu.Int8Linear(1280, 640, bias=True)
+    b.load_state_dict(sd)
+    b = b.to(DEV)
+    assert b.mode == "sparse" and b.weight_int8_nk.numel() == 0
+    assert torch.equal(a.weight_sparse_comp, b.weight_sparse_comp)
+    assert torch.equal(a.weight_sparse_meta, b.weight_sparse_meta)
+    x = torch.randn(300, 1280, device=DEV, dtype=torch.bfloat16)
+    assert torch.equal(a(x), b(x))

@@ -120,6 +120,14 @@ def test_state_dict_roundtrip_dense(qu):
     assert torch.equal(a.weight_int8_nk, b.weight_int8_nk) and torch.equal(a.weight_scale, b.weight_scale)
 
 
+def test_state_dict_carries_mode_and_epilogue(qu):
+    a = qu.Int8Linear.from_linear(nn.Linear(128, 64).bfloat16()).interleave_geglu_rows()
+    b = qu.Int8Linear(128, 64, bias=True)
+    b.load_state_dict(a.state_dict())
+    assert b.epilogue == "geglu" and b.mode == "tc" and b.weight_scale.dtype == torch.bfloat16
+    assert torch.equal(a.weight_int8_nk, b.weight_int8_nk) and torch.equal(a.bias, b.bias)
+
+
 def test_geglu_row_interleave(qu):
     lin = nn.Linear(128, 64).half()
     layer = qu.Int8Linear.from_linear(lin)
