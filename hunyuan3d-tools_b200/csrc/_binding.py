@@ -14,6 +14,7 @@ Outputs and workspaces are allocated here with torch (the C ABI never allocates)
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_int64, c_void_p
 
 import torch
@@ -33,6 +34,9 @@ SIGNATURES = {
     "hy3d_linear_w8a8_dense": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64,
                                c_int, c_int, c_int, c_void_p],
+    "hy3d_linear_w8a8_dense_fused": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int64,
+                                     c_int64, c_int64, c_int, c_int, c_void_p],
     "hy3d_linear_w8a8_dense_static": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                                       c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int,
                                       c_void_p],
@@ -60,6 +64,8 @@ def configure(lib: ctypes.CDLL) -> ctypes.CDLL:
     for name in ("hy3d_static_scratch_max_bytes", "hy3d_static_scratch_max_rows"):
         getattr(lib, name).restype = c_int64
         getattr(lib, name).argtypes = []
+    lib.hy3d_fused_sync_bytes.restype = ctypes.c_size_t
+    lib.hy3d_fused_sync_bytes.argtypes = [c_int64]
     lib.hy3d_arch.restype = ctypes.c_char_p
     lib.hy3d_arch.argtypes = []
     lib.hy3d_status_string.restype = ctypes.c_char_p
@@ -188,9 +194,55 @@ class TcGemmModule(_Base):
                 "hy3d_gemm_w8a8_dense")
         return out
 
+    # Hand-off counters of the fused quantise + GEMM kernel: one zeroed buffer per
+    # (device, stream); every launch leaves it zeroed, launches on one stream never overlap.
+    _sync_cache = {}
+
+    def _sync_buffer(self, x: torch.Tensor, M: int) -> torch.Tensor:
+        need = int(self._lib.hy3d_fused_sync_bytes(M)) // 4
+        key = (x.device.index, self._stream(x))
+        buf = self._sync_cache.get(key)
+        if buf is None or buf.numel() < need:
+            n = 4096
+            while n < need:
+                n *= 2
+            buf = torch.zeros(n, dtype=torch.int32, device=x.device)
+            self._sync_cache[key] = buf
+        return buf
+
+    def reset_fused_sync(self):
+        """Re-zeroes the hand-off counters (only needed after a device-side timeout)."""
+        for buf in self._sync_cache.values():
+            buf.zero_()
+
+    def int8_linear_tc_fused(self, x, w_int8, w_scale, bias, epilogue=EPI_LINEAR, block_n=0):
+        """``int8_linear_tc`` as one launch: the activation quantiser runs inside the GEMM
+        kernel (the role of the reference's fused path, csrc/int8_sparse_tc.cu:1934-2070).
+        Bit-identical to the two-launch path."""
+        self._req(x, "x", (torch.float16, torch.bfloat16), 2)
+        self._req(w_int8, "w_int8", torch.int8, 2)
+        M, K = x.shape
+        N = w_int8.shape[0]
+        if w_int8.shape[1] != K:
+            raise RuntimeError(f"K mismatch: x has {K}, w_int8 has {w_int8.shape[1]}")
+        q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+        s = torch.empty((M,), dtype=torch.float32, device=x.device)
+        out = torch.empty(self._out_shape(M, N, epilogue), dtype=x.dtype, device=x.device)
+        sync = self._sync_buffer(x, M)
+        bptr, bcode = self._opt_bias(bias)
+        with torch.cuda.device(x.device):
+            self._check(self._lib.hy3d_linear_w8a8_dense_fused(
+                x.data_ptr(), _DTYPE_CODE[x.dtype], K, q.data_ptr(), s.data_ptr(), sync.data_ptr(),
+                w_int8.data_ptr(), w_scale.data_ptr(), _DTYPE_CODE[w_scale.dtype], bptr, bcode,
+                out.data_ptr(), _DTYPE_CODE[x.dtype], M, N, K, epilogue, block_n,
+                self._stream(x)), "hy3d_linear_w8a8_dense_fused")
+        return out
+
     def int8_linear_tc(self, x, w_int8, w_scale, bias, epilogue=EPI_LINEAR, cta_group=0, block_n=0):
         """x (M,K) f16/bf16, w_int8 (N,K), w_scale (N), bias (N) or empty -> (M,N) in x's
         dtype.  csrc/int8_gemm_tc.cu:312-320."""
+        if cta_group == 0 and os.environ.get("HY3D_FUSED_QUANT", "0") == "1":
+            return self.int8_linear_tc_fused(x, w_int8, w_scale, bias, epilogue, block_n)
         self._req(x, "x", (torch.float16, torch.bfloat16), 2)
         self._req(w_int8, "w_int8", torch.int8, 2)
         M, K = x.shape

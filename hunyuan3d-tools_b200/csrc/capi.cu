@@ -173,6 +173,39 @@ int hy3d_linear_w8a8_dense(const void* x, int x_dtype, int64_t ldx, int8_t* q_ws
                     N, K, epilogue, cta_group, block_n, s);
 }
 
+size_t hy3d_fused_sync_bytes(int64_t M) {
+  if (M < 0) return 0;
+  return static_cast<size_t>(2 + (M + 127) / 128) * sizeof(int32_t);
+}
+
+int hy3d_linear_w8a8_dense_fused(const void* x, int x_dtype, int64_t ldx, int8_t* q_ws,
+                                 float* scale_ws, int32_t* sync_ws, const int8_t* B,
+                                 const void* w_scale, int w_scale_dtype, const void* bias,
+                                 int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
+                                 int64_t K, int epilogue, int block_n, void* stream) {
+  int rc = check_device();
+  if (rc != HY3D_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The in-kernel quantiser reads the activations in the output's 16-bit type from
+  // 16-byte-aligned rows; anything else takes the two-launch path (same results).
+  const bool can_fuse = x && sync_ws && x_dtype == out_dtype &&
+                        (x_dtype == HY3D_F16 || x_dtype == HY3D_BF16) && (ldx & 7) == 0 &&
+                        (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  if (!can_fuse) {
+    rc = quantize_rows(x, x_dtype, M, K, ldx, q_ws, scale_ws, s);
+    if (rc != HY3D_OK) return rc;
+    return gemm_dense(q_ws, B, scale_ws, w_scale, w_scale_dtype, bias, bias_dtype, out, out_dtype,
+                      M, N, K, epilogue, 1, block_n, s);
+  }
+  if (M > 0 && (!q_ws || !scale_ws)) return HY3D_ERR_ARG;
+  FusedInput f;
+  f.x = x;
+  f.ldx = ldx;
+  f.sync = sync_ws;
+  return gemm_dense(q_ws, B, scale_ws, w_scale, w_scale_dtype, bias, bias_dtype, out, out_dtype, M,
+                    N, K, epilogue, 1, block_n, s, &f);
+}
+
 int hy3d_prune_pack_24(const int8_t* w, int64_t N, int64_t K, int8_t* comp, uint8_t* meta_raw,
                        uint32_t* meta_packed, int64_t meta_ld, void* stream) {
   const int rc = check_device();

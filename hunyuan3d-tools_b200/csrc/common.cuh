@@ -60,6 +60,7 @@ enum DeviceError : int {
   kDevTimeoutStore = 105,
   kDevTimeoutPeer = 106,       // CTA-pair handshake
   kDevBadAlignment = 107,      // dynamic shared memory not 1024-byte aligned
+  kDevTimeoutQuant = 108,      // producer gave up waiting for a tile of the fused quantiser
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -6,9 +6,12 @@
 //     q     = clamp(rint(x / scale), -128, 127)    (IEEE division, round-half-even)
 // The row is read ONCE with 16-byte loads and kept in registers between the absmax
 // reduction and the rounding pass, so the kernel moves 2*K + K + 4/M bytes per row.
-// The division is done as x * rcp(scale) with a guard: whenever the product lands within
-// 1e-4 of a rounding boundary (k + 0.5) the element is redone with a true IEEE division, so
-// the result always equals rint(x / scale).
+// 16-bit activations sit on a coarse grid, so quotients within rounding error of k + 0.5 are
+// common (about 0.2 % of the elements of a Gaussian bf16 row) and their codes depend on the
+// last bit of the IEEE quotient.  The quotient is therefore computed exactly, without a
+// division instruction: q0 = x * rcp(scale) followed by two residual corrections
+// (r = fma(-q, scale, x); q = fma(r, rcp, q)), the sequence that yields the correctly
+// rounded x / scale when rcp is the correctly rounded reciprocal.
 #include "common.cuh"
 
 namespace hy3d {
@@ -34,31 +37,51 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   }
 }
 
+// Folds the eight 16-bit values of a 16-byte vector into a running packed |x| maximum
+// (two lanes per register), without widening them first.
+template <bool kBf16>
+__device__ __forceinline__ void absmax8(const uint4& v, uint32_t& acc) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t a = w[i] & 0x7FFF7FFFu;
+    if (kBf16) {
+      const __nv_bfloat162 m = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&acc),
+                                       *reinterpret_cast<const __nv_bfloat162*>(&a));
+      acc = *reinterpret_cast<const uint32_t*>(&m);
+    } else {
+      const __half2 m = __hmax2(*reinterpret_cast<const __half2*>(&acc),
+                                *reinterpret_cast<const __half2*>(&a));
+      acc = *reinterpret_cast<const uint32_t*>(&m);
+    }
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ float absmax_to_float(uint32_t acc) {
+  if (kBf16) {
+    return fmaxf(__uint_as_float(acc << 16), __uint_as_float(acc & 0xFFFF0000u));
+  }
+  const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&acc));
+  return fmaxf(t.x, t.y);
+}
+
 // Quantises eight values to eight int8 codes (two words).  Float <-> int conversion
-// instructions run at a fraction of the FMA rate on this architecture, so rounding uses the
-// 1.5 * 2^23 trick: adding that constant rounds |t| < 2^22 to the nearest integer (ties to
-// even, the FPU's own rounding) and leaves the two's-complement code in the low mantissa byte,
-// which a byte permute then gathers.  t = x * rcp(scale) differs from the IEEE quotient by
-// less than 3e-5 for |t| <= 128; whenever any of the eight lands within 1e-4 of a rounding
-// boundary the group is redone with true divisions, so the codes always equal rint(x / scale).
+// instructions run at a fraction of the FMA rate on this architecture, so the final rounding
+// uses the 1.5 * 2^23 trick: adding that constant rounds |t| < 2^22 to the nearest integer
+// (ties to even, the FPU's own rounding) and leaves the two's-complement code in the low
+// mantissa byte, which a byte permute then gathers.  t itself is the correctly rounded
+// quotient x / scale (see the file header), so the codes equal rint(x / scale).
 // No clamp is needed: scale = max|x| / 127 bounds |x / scale| by 127 (+ one rounding).
 __device__ __forceinline__ uint2 quant8(const float (&f)[8], float scale, float inv) {
   constexpr float kMagic = 12582912.0f;
-  float u[8];
-  float dev = 0.0f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float t = f[j] * inv;
-    u[j] = t + kMagic;
-    dev = fmaxf(dev, fabsf(t - (u[j] - kMagic)));
-  }
-  if (dev > 0.4999f) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) u[j] = rintf(__fdiv_rn(f[j], scale)) + kMagic;
-  }
   uint32_t b[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) b[j] = __float_as_uint(u[j]);
+  for (int j = 0; j < 8; ++j) {
+    float q = f[j] * inv;
+    q = fmaf(fmaf(-q, scale, f[j]), inv, q);
+    q = fmaf(fmaf(-q, scale, f[j]), inv, q);
+    b[j] = __float_as_uint(q + kMagic);
+  }
   const uint32_t p01 = __byte_perm(b[0], b[1], 0x0040), p23 = __byte_perm(b[2], b[3], 0x0040);
   const uint32_t p45 = __byte_perm(b[4], b[5], 0x0040), p67 = __byte_perm(b[6], b[7], 0x0040);
   return make_uint2(__byte_perm(p01, p23, 0x5410), __byte_perm(p45, p67, 0x5410));
@@ -81,7 +104,7 @@ quantize_rows_kernel(const uint16_t* __restrict__ x, int64_t ldx, int8_t* __rest
   const int nvec = K >> 3;
 
   uint4 v[kMaxV];
-  float amax = 0.0f;
+  uint32_t amax2 = 0;
   const uint4* src = reinterpret_cast<const uint4*>(x + (row_ok ? row : 0) * ldx);
 #pragma unroll
   for (int i = 0; i < kMaxV; ++i) {
@@ -93,12 +116,8 @@ quantize_rows_kernel(const uint16_t* __restrict__ x, int64_t ldx, int8_t* __rest
     }
   }
 #pragma unroll
-  for (int i = 0; i < kMaxV; ++i) {
-    float f[8];
-    unpack8<kBf16>(v[i], f);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
-  }
+  for (int i = 0; i < kMaxV; ++i) absmax8<kBf16>(v[i], amax2);
+  float amax = absmax_to_float<kBf16>(amax2);
   // Reduce over the G threads of the row.
   const int w = G < 32 ? G : 32;
   for (int off = w >> 1; off > 0; off >>= 1)

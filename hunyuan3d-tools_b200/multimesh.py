@@ -112,14 +112,17 @@ class GraphedStep:
 
 
 def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed: int = 0, fuse_geglu=True,
-                       verbose=False, **unet_kwargs):
+                       fuse_qkv=True, channels_last=True, verbose=False, **unet_kwargs):
     """Random-init UNet of the paint configuration with its Linears swapped for INT8 layers.
     ``quant``: "mixed" (2:4 sparse where K >= 640, dense elsewhere), "dense", "sparse" (the
-    reference's sparse mode: small-K layers stay bf16) or "none"."""
+    reference's sparse mode: small-K layers stay bf16) or "none".  ``fuse_qkv`` stacks the
+    q/k/v (self-attention) and k/v (cross-attention) projections that share an input."""
     from . import quantize_utils as qu
-    from .unet import UNetSD21MV, fuse_geglu_layers
+    from .unet import UNetSD21MV, fuse_geglu_layers, fuse_qkv_layers
     torch.manual_seed(seed)
     unet = UNetSD21MV(**unet_kwargs).to(dtype).to(device).eval()
+    if channels_last:
+        unet.use_channels_last()
     stats = {}
     if quant == "mixed":
         stats = qu.quantize_model_mixed(unet, verbose=verbose)
@@ -131,6 +134,8 @@ def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed:
         raise ValueError(f"unknown quant mode {quant!r}")
     if fuse_geglu and quant in ("mixed", "dense"):
         stats["geglu_fused"] = fuse_geglu_layers(unet)
+    if fuse_qkv and quant != "none":
+        stats["qkv_layers_removed"] = fuse_qkv_layers(unet)
     return unet, stats
 
 

@@ -204,6 +204,37 @@ class Int8Linear(nn.Module):
         super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys,
                                       unexpected_keys, error_msgs)
 
+    @staticmethod
+    def concat(layers) -> "Int8Linear":
+        """One layer computing ``[l0(x) | l1(x) | ...]`` for already converted layers that read
+        the same input (q/k/v projections): the per-row weight codes, scales, 2:4 metadata and
+        biases are stacked along the output dimension, so every output column keeps the bits
+        the separate layer would have produced while the activation is quantised once."""
+        layers = list(layers)
+        first = layers[0]
+        for l in layers:
+            if not isinstance(l, Int8Linear):
+                raise TypeError("Int8Linear.concat takes Int8Linear layers")
+            if (l.in_features != first.in_features or l.mode != first.mode or l.epilogue != "linear"
+                    or (l.bias is None) != (first.bias is None)
+                    or l.weight_scale.dtype != first.weight_scale.dtype):
+                raise RuntimeError("Int8Linear.concat needs layers of the same in_features, mode, "
+                                   "dtype and bias presence with the plain linear epilogue")
+        n = sum(l.out_features for l in layers)
+        out = Int8Linear(first.in_features, n, bias=first.bias is not None, dtype=first.weight_scale.dtype)
+        out.weight_scale = torch.cat([l.weight_scale for l in layers]).contiguous()
+        if first.bias is not None:
+            out.bias = torch.cat([l.bias for l in layers]).contiguous()
+        if first.mode == "sparse":
+            out.weight_sparse_comp = torch.cat([l.weight_sparse_comp for l in layers]).contiguous()
+            out.weight_sparse_meta = torch.cat([l.weight_sparse_meta for l in layers]).contiguous()
+            out.register_buffer("weight_int8_nk", torch.empty(0, dtype=torch.int8,
+                                                              device=first.weight_scale.device))
+        else:
+            out.weight_int8_nk = torch.cat([l.weight_int8_nk for l in layers]).contiguous()
+        out.mode = first.mode
+        return out
+
     def interleave_geglu_rows(self) -> "Int8Linear":
         """Re-orders a GEGLU up-projection ([value(H) | gate(H)] output rows) into blocks of
         16 value rows followed by their 16 gate rows and switches the layer to the fused

@@ -63,13 +63,26 @@ class Attention(nn.Module):
         self.to_k = nn.Linear(ctx, dim, bias=False)
         self.to_v = nn.Linear(ctx, dim, bias=False)
         self.to_out = nn.Linear(dim, dim)
+        self.to_qkv = None    # set by fuse_qkv_layers
+        self.to_kv = None
+        self.is_self = context_dim is None
 
     def forward(self, x, context=None):
-        context = x if context is None else context
         b, n, c = x.shape
-        q = self.to_q(x).view(b, n, self.heads, c // self.heads).transpose(1, 2)
-        k = self.to_k(context).view(b, context.shape[1], self.heads, c // self.heads).transpose(1, 2)
-        v = self.to_v(context).view(b, context.shape[1], self.heads, c // self.heads).transpose(1, 2)
+        if self.to_qkv is not None:           # self-attention with the three projections stacked
+            q, k, v = self.to_qkv(x).split(c, dim=-1)
+            m = n
+        else:
+            context = x if context is None else context
+            m = context.shape[1]
+            q = self.to_q(x)
+            if self.to_kv is not None:
+                k, v = self.to_kv(context).split(c, dim=-1)
+            else:
+                k, v = self.to_k(context), self.to_v(context)
+        q = q.view(b, n, self.heads, c // self.heads).transpose(1, 2)
+        k = k.view(b, m, self.heads, c // self.heads).transpose(1, 2)
+        v = v.view(b, m, self.heads, c // self.heads).transpose(1, 2)
         o = F.scaled_dot_product_attention(q, k, v)
         return self.to_out(o.transpose(1, 2).reshape(b, n, c))
 
@@ -197,12 +210,22 @@ class UNetSD21MV(nn.Module):
 
         self.norm_out = nn.GroupNorm(32, ch[0], eps=1e-5)
         self.conv_out = nn.Conv2d(ch[0], out_channels, 3, padding=1)
+        # NHWC activations: the convolutions run without layout conversions and the token
+        # view (B, H*W, C) the transformer blocks take is free.  Set by use_channels_last().
+        self.channels_last = False
+
+    def use_channels_last(self) -> "UNetSD21MV":
+        self.to(memory_format=torch.channels_last)
+        self.channels_last = True
+        return self
 
     def forward(self, x, t, context):
         """x: (B*views, 4, H, W); t: (B*views,) or scalar tensor; context: (B*views, 77, 1024)."""
         if t.dim() == 0:
             t = t.expand(x.shape[0])
         temb = self.time_embedding(timestep_embedding(t, self.time_proj_dim).to(x.dtype))
+        if self.channels_last:
+            x = x.contiguous(memory_format=torch.channels_last)
         h = self.conv_in(x)
         skips = [h]
         for layer in self.down:
@@ -220,7 +243,7 @@ class UNetSD21MV(nn.Module):
                 h = layer["attn"](h, context)
             if "up" in layer:
                 h = layer["up"](h)
-        return self.conv_out(F.silu(self.norm_out(h)))
+        return self.conv_out(F.silu(self.norm_out(h))).contiguous()
 
 
 def fuse_geglu_layers(model: nn.Module) -> int:
@@ -234,6 +257,30 @@ def fuse_geglu_layers(model: nn.Module) -> int:
             m.proj.interleave_geglu_rows()
             n += 1
     return n
+
+
+def fuse_qkv_layers(model: nn.Module) -> int:
+    """Stacks the ``Int8Linear`` projections that read the same activation: q/k/v of every
+    self-attention into one layer, k/v of every cross-attention into one.  The activation is
+    then quantised once instead of three (two) times and one GEMM replaces three (two); every
+    output column keeps its bits.  Returns the number of layers removed."""
+    from .quantize_utils import Int8Linear
+    removed = 0
+    for m in model.modules():
+        if not isinstance(m, Attention) or m.to_qkv is not None or m.to_kv is not None:
+            continue
+        group = [m.to_q, m.to_k, m.to_v] if m.is_self else [m.to_k, m.to_v]
+        if not all(isinstance(l, Int8Linear) and l.epilogue == "linear" for l in group):
+            continue
+        if len({l.mode for l in group}) != 1:
+            continue
+        fused = Int8Linear.concat(group)
+        if m.is_self:
+            m.to_qkv, m.to_q, m.to_k, m.to_v = fused, None, None, None
+        else:
+            m.to_kv, m.to_k, m.to_v = fused, None, None
+        removed += len(group) - 1
+    return removed
 
 
 # -----------------------------------------------------------------------------------------

@@ -96,6 +96,28 @@ int hy3d_linear_w8a8_dense(const void* x, int x_dtype, int64_t ldx,
                            int epilogue, int cta_group, int block_n, void* stream);
 
 /*
+ * The same layer as ONE kernel: the activation quantiser runs inside the GEMM kernel (idle
+ * epilogue warps quantise rows of x into q_ws / scale_ws eight at a time, the TMA producers
+ * pick each 128-row tile up from L2 as soon as it is complete), so the int8 activations never
+ * make the round trip through HBM between two launches.  Results are bit-identical to
+ * hy3d_linear_w8a8_dense.  sync_ws: hy3d_fused_sync_bytes(M) bytes of int32 counters that
+ * must be ZERO before the first use; every launch leaves them zero again, so one buffer per
+ * stream can be reused by all layers (launches that may overlap need separate buffers; after a
+ * device-side timeout re-zero it).  x_dtype must equal out_dtype and ldx % 8 == 0 for the
+ * fused kernel; other combinations run the two-launch path.  cta_group is always 1.
+ * Replaces: the fused quantise + GEMM path csrc/int8_sparse_tc.cu:657-734, 1934-2070
+ * (sparse_gemm_fq_kernel, sparse_fq_launch) in its role, for the dense layer.
+ */
+size_t hy3d_fused_sync_bytes(int64_t M);
+int hy3d_linear_w8a8_dense_fused(const void* x, int x_dtype, int64_t ldx,
+                                 int8_t* q_ws, float* scale_ws, int32_t* sync_ws,
+                                 const int8_t* B, const void* w_scale, int w_scale_dtype,
+                                 const void* bias, int bias_dtype,
+                                 void* out, int out_dtype,
+                                 int64_t M, int64_t N, int64_t K,
+                                 int epilogue, int block_n, void* stream);
+
+/*
  * The dense linear layer again, for callers that may not allocate device memory where the
  * layer runs (an allocation-free region of a render or capture loop, a sandboxed plugin that
  * is only handed pre-registered buffers, a process whose device pool belongs to another

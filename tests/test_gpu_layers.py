@@ -173,3 +173,27 @@ def test_sparse_state_dict_roundtrip(qu):
     assert torch.equal(a.weight_sparse_meta, b.weight_sparse_meta)
     x = torch.randn(300, 1280, device=DEV, dtype=torch.bfloat16)
     assert torch.equal(a(x), b(x))
+
+
+def test_host_pipeline_matches_direct_calls(qu, pkg):
+    """Layers fed from pinned host memory through the three-stream pipeline return the same
+    bits as direct calls on device tensors."""
+    import importlib
+    host_io = importlib.import_module(pkg.__name__ + ".host_io")
+    torch.manual_seed(4)
+    shapes = [(1000, 320, 640), (513, 640, 320), (2048, 1280, 1280)]
+    layers, hx, hy, ref = [], [], [], []
+    for M, K, N in shapes:
+        lin = torch.nn.Linear(K, N, device=DEV, dtype=torch.bfloat16)
+        L = qu.Int8Linear.from_linear(lin)
+        x = torch.randn(M, K).bfloat16()
+        layers.append(L)
+        hx.append(x.pin_memory())
+        hy.append(torch.empty(M, N, dtype=torch.bfloat16).pin_memory())
+        ref.append(L(x.to(DEV)).cpu())
+    pipe = host_io.HostPipeline(DEV)
+    for _ in range(2):
+        pipe.run(layers, hx, hy)
+    pipe.synchronize()
+    for a, b in zip(hy, ref):
+        assert torch.equal(a, b)

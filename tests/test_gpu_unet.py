@@ -89,6 +89,22 @@ def test_reduced_unet_ten_steps_matches_oracle_linears():
     assert O.rel_l2(a, b) < 2e-2          # the stated gate on latents after 10 steps
 
 
+def test_stacked_qkv_projections_keep_every_bit():
+    """q/k/v stacked into one layer: one quantise + one GEMM, outputs bit-identical to the
+    separate layers for the dense and the 2:4 sparse kernels."""
+    mm = importlib.import_module(PKG_NAME + ".multimesh")
+    for quant in ("dense", "mixed"):
+        a, sa = mm.build_texture_unet(DEV, torch.bfloat16, quant, seed=2, fuse_qkv=False, **SMALL)
+        b, sb = mm.build_texture_unet(DEV, torch.bfloat16, quant, seed=2, fuse_qkv=True, **SMALL)
+        assert "qkv_layers_removed" not in sa and sb["qkv_layers_removed"] > 0
+        g = torch.Generator().manual_seed(3)
+        x = torch.randn(4, 4, 16, 16, generator=g).bfloat16().to(DEV)
+        ctx = torch.randn(4, 7, 128, generator=g).bfloat16().to(DEV)
+        t = torch.full((4,), 300, device=DEV)
+        with torch.no_grad():
+            assert torch.equal(a(x, t, ctx), b(x, t, ctx))
+
+
 def test_graphed_step_equals_eager():
     mm = importlib.import_module(PKG_NAME + ".multimesh")
     un = importlib.import_module(PKG_NAME + ".unet")

@@ -29,7 +29,8 @@ def test_binding_table_covers_header(build_mod):
     binding = __import__("importlib").import_module("hunyuan3d-tools_b200.csrc._binding")
     declared = set(_declared_symbols())
     bound = set(binding.SIGNATURES) | {"hy3d_arch", "hy3d_status_string",
-                                       "hy3d_static_scratch_max_bytes", "hy3d_static_scratch_max_rows"}
+                                       "hy3d_static_scratch_max_bytes", "hy3d_static_scratch_max_rows",
+                                       "hy3d_fused_sync_bytes"}
     assert declared == bound
 
 
@@ -126,6 +127,32 @@ def test_state_dict_carries_mode_and_epilogue(qu):
     b.load_state_dict(a.state_dict())
     assert b.epilogue == "geglu" and b.mode == "tc" and b.weight_scale.dtype == torch.bfloat16
     assert torch.equal(a.weight_int8_nk, b.weight_int8_nk) and torch.equal(a.bias, b.bias)
+
+
+def test_concat_stacks_rows_scales_and_bias(qu):
+    torch.manual_seed(3)
+    lins = [torch.nn.Linear(128, n, bias=True) for n in (128, 256, 128)]
+    layers = [qu.Int8Linear.from_linear(l) for l in lins]
+    cat = qu.Int8Linear.concat(layers)
+    assert cat.out_features == 512 and cat.in_features == 128 and cat.mode == "tc"
+    assert torch.equal(cat.weight_int8_nk, torch.cat([l.weight_int8_nk for l in layers]))
+    assert torch.equal(cat.weight_scale, torch.cat([l.weight_scale for l in layers]))
+    assert torch.equal(cat.bias, torch.cat([l.bias for l in layers]))
+    with pytest.raises(RuntimeError):
+        qu.Int8Linear.concat([layers[0], qu.Int8Linear.from_linear(torch.nn.Linear(256, 128))])
+
+
+def test_qkv_fusion_rewires_attention(qu, pkg):
+    import importlib
+    un = importlib.import_module(pkg.__name__ + ".unet")
+    torch.manual_seed(0)
+    blk = un.TransformerBlock(128, 2, 128, 2)
+    qu.quantize_model_tensorcore(blk, verbose=False)
+    removed = un.fuse_qkv_layers(blk)
+    assert removed == 2 + 2 + 1           # two self-attentions (q,k,v -> 1) and one cross-attention (k,v -> 1)
+    assert blk.attn1.to_qkv.out_features == 384 and blk.attn1.to_q is None
+    assert blk.attn2.to_kv.out_features == 256 and blk.attn2.to_q is not None
+    assert un.fuse_qkv_layers(blk) == 0   # idempotent
 
 
 def test_geglu_row_interleave(qu):
