@@ -294,13 +294,29 @@ def run_ours(args):
         del a8, b8
     except Exception:
         pass
+    # The sweep mixes tensor-bound and HBM-bound shapes: sum over shapes of the larger of
+    # (ops / tensor peak) and (algorithmic GEMM bytes / measured copy bandwidth) is the time
+    # a kernel sitting on both rooflines would need for the same step.
+    hbm_gbs = peaks.get("hbm_gbs", 6650.0)
+    t_bound = 0.0
+    n_hbm_bound = 0
+    for (M, K, N) in SWEEP:
+        w_bytes = N * K * (0.625 if sparse else 1.0)
+        t_tc = 2.0 * M * K * N / (int8_peak * 1e12)
+        t_mem = (M * K + w_bytes + 4 * M + 4 * N + 2 * M * N) / (hbm_gbs * 1e9)
+        t_bound += max(t_tc, t_mem)
+        n_hbm_bound += 1 if t_mem > t_tc else 0
     roofline = {"bound": "tensor", "kernel": "gemm_sparse_kernel" if sparse else "gemm_dense_kernel",
                 "achieved": round(gemm_tops, 1), "peak": round(int8_peak, 1), "unit": "TOP/s",
                 "frac": round(gemm_tops / int8_peak, 4), "peak_source": peak_src,
                 "traffic": TRAFFIC_BYTES_PER_LAUNCH["sparse" if sparse else "dense"],
                 "traffic_source": "ncu dram bytes of one launch (profiles/), scaled by the sweep's algorithmic bytes",
                 "library_int8_gemm_8192_tops": lib_int8,
-                "launches_per_step": len(SWEEP), "avg_launch_us": round(ms_gemm * 1e3 / len(SWEEP), 2)}
+                "launches_per_step": len(SWEEP), "avg_launch_us": round(ms_gemm * 1e3 / len(SWEEP), 2),
+                "per_shape_bound": {"ms_per_step_at_bound": round(t_bound * 1e3, 4),
+                                    "frac_of_bound": round(t_bound / (ms_gemm * 1e-3), 4),
+                                    "hbm_bound_shapes": n_hbm_bound, "shapes": len(SWEEP),
+                                    "note": "sum over shapes of max(ops / peak, algorithmic bytes / measured copy GB/s)"}}
 
     # End to end through the public module API with host buffers.
     e2e = None

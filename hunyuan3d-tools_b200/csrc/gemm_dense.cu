@@ -714,11 +714,23 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
     return HY3D_ERR_SHAPE;
 
   if (block_n == 0) {
-    // Widest tile (multiple of 32 so the TMA-store epilogue applies) that divides N evenly;
-    // otherwise the widest one with a ragged last tile.
-    block_n = N >= 256 ? 256 : static_cast<int>(N);
-    for (int bn = 256; bn >= 128; bn -= 32) {
-      if (N >= bn && N % bn == 0) { block_n = bn; break; }
+    if (N <= 128) {
+      block_n = static_cast<int>(N);
+    } else {
+      // Tile width (a multiple of the TMA-store slab) that minimises rounds x time per tile,
+      // where rounds = ceil(tiles / SMs) and a tile costs its width plus a fixed per-stage
+      // overhead worth ~94 columns of MMA time (measured).  A last tile that sticks out of N
+      // is zero-filled on load and clipped on store.
+      const int sms = device_sm_count();
+      const int64_t m_tiles = (M + kTileM - 1) / kTileM;
+      const int step = geglu ? 64 : 32;
+      int64_t best = -1;
+      for (int bn = 256; bn >= 128; bn -= step) {
+        const int64_t tiles = m_tiles * ((N + bn - 1) / bn);
+        const int64_t rounds = (tiles + (sms > 0 ? sms : 148) - 1) / (sms > 0 ? sms : 148);
+        const int64_t cost = rounds * (bn + 94);
+        if (best < 0 || cost < best) { best = cost; block_n = bn; }
+      }
     }
   }
   if (block_n < 16 || block_n > 256 || (block_n & 15) || (geglu && (block_n & 31)))

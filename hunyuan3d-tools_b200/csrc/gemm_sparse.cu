@@ -211,15 +211,23 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const int n = w0 + row_in_tile;
       const bool n_ok = n < p.N;
       float ws = 0.0f, bs = 0.0f;
+      float sc_next = 0.0f;
       if (p.out_dtype != HY3D_S32) {
-        for (int c = et; c < p.block_t; c += kEpiThreads)
-          ctrl->as[buf][c] = (t0 + c) < p.M ? p.act_scale[t0 + c] : 0.0f;
+        if (p.tma_store) {
+          // Each warp stages the 32 token scales of its own slab (fetched one slab ahead), so
+          // the tile needs no CTA-wide barrier.
+          const int t = t0 + half * kSlabTokens + lane;
+          if (half * kSlabTokens < p.block_t && t < p.M) sc_next = p.act_scale[t];
+        } else {
+          for (int c = et; c < p.block_t; c += kEpiThreads)
+            ctrl->as[buf][c] = (t0 + c) < p.M ? p.act_scale[t0 + c] : 0.0f;
+        }
         if (n_ok) {
           ws = load_scalar(p.w_scale, p.ws_dtype, n);
           bs = p.bias ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
         }
       }
-      epi_bar_sync();
+      if (!p.tma_store) epi_bar_sync();
       if (ok) ok = mbar_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag,
                              kDevTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
@@ -229,6 +237,7 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                              static_cast<uint32_t>(buf * p.block_t);
       const float* asb = ctrl->as[buf];
       if (p.tma_store) {
+        float* asw = &ctrl->as[0][0] + (warp - 2) * kSlabTokens;   // this warp's 32 scales
         // Slabs of 32 tokens; this thread owns output column n, the warp 32 adjacent columns,
         // so a slab is a 32 (tokens) x 64 B block of the output, staged with 64-byte swizzle.
         const int nslab = p.block_t / kSlabTokens;
@@ -237,13 +246,21 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         for (int s = half; s < nslab; s += kWarpsPerQuarter) {
           const int c0 = s * kSlabTokens;
           uint32_t r[32];
+          const float sc = sc_next;
+          {
+            const int sn = s + kWarpsPerQuarter;
+            const int t = t0 + sn * kSlabTokens + lane;
+            sc_next = (sn < nslab && t < p.M) ? p.act_scale[t] : 0.0f;
+          }
           __syncwarp();
+          asw[lane] = sc;
           tmem_ld_x32(t_row + c0, r);
           tmem_ld_wait();
+          __syncwarp();
           float y[32];
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            const float4 a4 = *reinterpret_cast<const float4*>(asb + c0 + 4 * q);
+            const float4 a4 = *reinterpret_cast<const float4*>(asw + 4 * q);
             y[4 * q + 0] = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])), a4.x * ws, bs);
             y[4 * q + 1] = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 1])), a4.y * ws, bs);
             y[4 * q + 2] = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])), a4.z * ws, bs);
@@ -256,19 +273,16 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           if (lane == 0) tma_store_wait_read<0>();
           __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            // token row j of the slab: 64 B; 16-byte chunk c sits at c ^ ((j >> 1) & 3)
+          for (int j = 0; j < 32; j += 2) {
+            // token rows j, j+1 of the slab (64 B each): 16-byte chunk c of row j sits at
+            // c ^ ((j >> 1) & 3), the same for both rows of a pair; one conversion packs both.
             const uint32_t addr = stage_buf + static_cast<uint32_t>(j) * 64u +
                                   ((chunk ^ ((static_cast<uint32_t>(j) >> 1) & 3u)) << 4) + in_chunk;
-            uint16_t h;
-            if (p.out_dtype == HY3D_BF16) {
-              __nv_bfloat16 v = __float2bfloat16_rn(y[j]);
-              h = *reinterpret_cast<uint16_t*>(&v);
-            } else {
-              __half v = __float2half_rn(y[j]);
-              h = *reinterpret_cast<uint16_t*>(&v);
-            }
-            asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(h) : "memory");
+            const uint32_t pr = pack2(y[j], y[j + 1], p.out_dtype);
+            const uint16_t lo = static_cast<uint16_t>(pr & 0xFFFFu);
+            const uint16_t hi = static_cast<uint16_t>(pr >> 16);
+            asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(lo) : "memory");
+            asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr + 64u), "h"(hi) : "memory");
           }
           fence_proxy_async_smem();
           __syncwarp();
@@ -362,9 +376,18 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
     return HY3D_ERR_SHAPE;
 
   if (block_t == 0) {
-    // Measured on B200: short-K layers are bound by the output write and like the wider
-    // token tile; deeper K needs a third pipeline stage, which fits with 160 tokens.
-    block_t = K <= 640 ? 192 : 160;
+    // Token-tile width that minimises rounds x time per tile: rounds = ceil(tiles / SMs), a
+    // tile costs its width plus a fixed overhead worth ~94 columns of MMA time (the same
+    // model as the dense kernel; measured on B200 the widest tile wins whenever the grid is
+    // full, the narrowest when the whole problem is a single round).
+    const int sms = device_sm_count() > 0 ? device_sm_count() : 148;
+    const int64_t w_tiles = (N + kTileW - 1) / kTileW;
+    int64_t best = -1;
+    for (int bt = 224; bt >= 128; bt -= 32) {
+      const int64_t tiles = w_tiles * ((M + bt - 1) / bt);
+      const int64_t cost = ((tiles + sms - 1) / sms) * (bt + 94);
+      if (best < 0 || cost < best) { best = cost; block_t = bt; }
+    }
     if (M < block_t) block_t = static_cast<int>((M + 31) / 32 * 32);
   }
   if (block_t < 16 || block_t > kMaxBlockT || (block_t & 15)) return HY3D_ERR_SHAPE;
