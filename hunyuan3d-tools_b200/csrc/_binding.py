@@ -28,6 +28,7 @@ _DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32, tor
 # check that the library exports exactly what the header declares.
 SIGNATURES = {
     "hy3d_quantize_rows": [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p],
+    "hy3d_quantizer_enum_check": [c_int, c_void_p, c_void_p, c_void_p],
     "hy3d_gemm_w8a8_dense": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                              c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int,
                              c_void_p],
@@ -128,6 +129,14 @@ class _Base:
                                                      q.data_ptr(), s.data_ptr(), self._stream(x)),
                         "hy3d_quantize_rows")
         return q, s
+
+    def quantizer_enum_check(self, dtype):
+        """(pairs checked, codes differing from rint(x / scale)) over every 16-bit (amax, x)."""
+        pairs, bad = ctypes.c_ulonglong(0), ctypes.c_ulonglong(0)
+        self._check(self._lib.hy3d_quantizer_enum_check(
+            _DTYPE_CODE[dtype], ctypes.byref(pairs), ctypes.byref(bad),
+            torch.cuda.current_stream().cuda_stream), "hy3d_quantizer_enum_check")
+        return pairs.value, bad.value
 
     def _out_shape(self, M, N, epilogue):
         return (M, N // 2) if epilogue == EPI_GEGLU else (M, N)

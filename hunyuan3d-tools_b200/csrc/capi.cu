@@ -149,6 +149,13 @@ int hy3d_quantize_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t
   return quantize_rows(x, x_dtype, M, K, ldx, q, scale, static_cast<cudaStream_t>(stream));
 }
 
+int hy3d_quantizer_enum_check(int x_dtype, unsigned long long* pairs_out,
+                              unsigned long long* mismatches_out, void* stream) {
+  const int rc = check_device();
+  if (rc != HY3D_OK) return rc;
+  return quantizer_enum_check(x_dtype, pairs_out, mismatches_out, static_cast<cudaStream_t>(stream));
+}
+
 int hy3d_gemm_w8a8_dense(const int8_t* A, const int8_t* B, const float* act_scale,
                          const void* w_scale, int w_scale_dtype, const void* bias, int bias_dtype,
                          void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int epilogue,

@@ -739,7 +739,13 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   // CTA pairs need an even split of the B tile into two multiples of 16 rows.
   int group = cta_group;
   if (group == 0) {
-    if (const char* e = getenv("HY3D_CTA_GROUP")) group = atoi(e) == 2 ? 2 : 1; else group = 1;
+    // CTA pairs halve the B traffic into shared memory, which is what bounds the tensor pipe
+    // on deep-K problems (measured: 8192^3 2768 vs 2332 TOPS); they pay off once the grid
+    // holds several rounds of 256-row tile pairs, and cost a little on short-K or small grids.
+    const int sms = device_sm_count() > 0 ? device_sm_count() : 148;
+    const int64_t pair_tiles = ((M + 2 * kTileM - 1) / (2 * kTileM)) * ((N + block_n - 1) / block_n);
+    group = (!fused && K >= 1024 && (block_n & 31) == 0 && pair_tiles >= 4 * (sms / 2)) ? 2 : 1;
+    if (const char* e = getenv("HY3D_CTA_GROUP")) group = atoi(e) == 2 ? 2 : 1;
   }
   if (fused) {
     if (out_dtype == HY3D_S32 || !fused->x || !fused->sync || (K & 7) || (fused->ldx & 7) ||

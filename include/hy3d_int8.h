@@ -12,6 +12,7 @@
 #ifndef HY3D_INT8_H_
 #define HY3D_INT8_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -59,6 +60,16 @@ int hy3d_last_device_status(int* status_out);
  */
 int hy3d_quantize_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
                        int8_t* q, float* scale, void* stream);
+
+/*
+ * Self-check of the quantiser's rounding (test hook, no reference counterpart).  The kernel
+ * above never divides; this call enumerates on the device every pair of 16-bit patterns
+ * (amax, x) of x_dtype with |x| <= amax -- every input the quantiser can meet -- and counts the
+ * pairs whose code differs from (int8) rint(x / scale) computed with IEEE divisions.
+ * Synchronises the stream; *mismatches_out must come back 0 (about 1e9 pairs, ~0.1 s).
+ */
+int hy3d_quantizer_enum_check(int x_dtype, unsigned long long* pairs_out,
+                              unsigned long long* mismatches_out, void* stream);
 
 /*
  * Dense W8A8 GEMM with fused epilogue.

@@ -27,6 +27,16 @@ def test_quantize_rows_bit_exact(ik, dtype, M, K):
     assert torch.equal(q.cpu(), qo)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_quantizer_rounding_is_exact_for_every_16_bit_input(ik, dtype):
+    """The kernel refines x * rcp(scale) instead of dividing.  Its inputs are 16-bit, so the
+    claim "codes equal rint(x / scale)" is checked by enumeration on the device: every amax
+    pattern x every x pattern with |x| <= amax, against IEEE division."""
+    pairs, bad = ik.quantizer_enum_check(dtype)
+    assert pairs > 1_000_000_000
+    assert bad == 0
+
+
 def test_quantize_rounding_boundaries(ik):
     """Values that sit exactly on, or one ulp beside, a x.5 quotient."""
     K = 256
