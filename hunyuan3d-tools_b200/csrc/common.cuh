@@ -300,6 +300,31 @@ __device__ __forceinline__ void mma_i8_2cta(uint32_t d_tmem, uint64_t desc_a, ui
       ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same instructions with each descriptor given as (low word, shared high word): the
+// issuing thread then advances a 32-bit address field instead of doing 64-bit arithmetic.
+template <int kG>
+__device__ __forceinline__ void mma_i8_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                            uint32_t desc_hi, uint32_t idesc, uint32_t accumulate) {
+  if (kG == 1) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
 // One 2:4-sparse int8 MMA: A compressed in smem, its metadata at e_tmem.
 __device__ __forceinline__ void mma_sp_i8_1cta(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b,
                                                uint32_t e_tmem, uint32_t idesc,

@@ -327,7 +327,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
-      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kG * kEpiThreads);
+      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kG * kEpiWarps);   // one arrival per epilogue warp
     }
     ctrl->abort_flag = 0;
     fence_barrier_init();
@@ -400,11 +400,37 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // probe, four issues and one commit per stage.
     if (lane == 0 && leader) {
       const uint32_t idesc = make_idesc_i8(kTileM * kG, static_cast<uint32_t>(p.block_n), false);
-      const uint64_t desc_hi = make_smem_desc(0, 1024, 128);      // everything but the address
+      // Descriptor = (low word: address field + leading-dimension offset, high word: stride,
+      // version, swizzle).  Only the 14-bit address field changes from stage to stage and from
+      // K step to K step (+2 per 32 bytes), and it never carries out of its field, so the loop
+      // keeps one running low word per operand.
+      const uint64_t desc_const = make_smem_desc(0, 1024, 128);
+      const uint32_t desc_hi = static_cast<uint32_t>(desc_const >> 32);
+      const uint32_t lo_const = static_cast<uint32_t>(desc_const);
+      const uint32_t a_lo0 = lo_const | ((smem_base & 0x3FFFFu) >> 4);
+      const uint32_t stage_step = stage_bytes >> 4;
+      const uint32_t b_off = a_bytes >> 4;
+      const bool do_mma = !(p.debug & 4);
+      const int full_kb = p.last_ksteps == 4 ? p.num_kb : p.num_kb - 1;   // stages with 4 K steps
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t a_lo = a_lo0;
       bool ok = true;
       int it = 0;
+      auto next_stage = [&]() {
+        a_lo += stage_step;
+        if (++stage == p.stages) { stage = 0; phase ^= 1; a_lo = a_lo0; }
+      };
+      auto wait_full = [&]() {
+        const uint32_t bar = smem_u32(&ctrl->full[stage]);
+        if (mbar_test_wait(bar, phase)) return true;
+        return mbar_wait<true>(bar, phase, abort_flag, kDevTimeoutFull);
+      };
+      auto commit_empty = [&]() {
+        // Frees the stage (in both CTAs of a pair) once these MMAs have read it.
+        if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
+        else tc_commit_2cta(smem_u32(&ctrl->empty[stage]), 3);
+      };
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
@@ -414,33 +440,32 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         tc_fence_after_sync();
         HY3D_TRACE_EVENT(1, tr, 6, it);
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.acc_cols);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, kDevTimeoutFull);
+        uint32_t acc = 0;   // the first MMA of a tile overwrites the accumulator
+        for (int kb = 0; kb < full_kb; ++kb) {
+          ok = wait_full();
           if (!ok) break;
-          const uint32_t sa = smem_base + stage * stage_bytes;
-          // Each K step of 32 int8 is 32 bytes further along the swizzled row: +2 in the
-          // descriptor's 16-byte address units.
-          const uint64_t da = desc_hi | static_cast<uint64_t>((sa & 0x3FFFFu) >> 4);
-          const uint64_t db = desc_hi | static_cast<uint64_t>(((sa + a_bytes) & 0x3FFFFu) >> 4);
-          const int nk = (kb == p.num_kb - 1) ? p.last_ksteps : 4;
-          if (!(p.debug & 4)) {
-            if (nk == 4) {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                if (kG == 1) mma_i8_1cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                else mma_i8_2cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-              }
-            } else {
-              for (int k = 0; k < nk; ++k) {
-                if (kG == 1) mma_i8_1cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                else mma_i8_2cta(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          if (do_mma) {
+            mma_i8_lohi<kG>(d_tmem, a_lo, a_lo + b_off, desc_hi, idesc, acc);
+            mma_i8_lohi<kG>(d_tmem, a_lo + 2, a_lo + b_off + 2, desc_hi, idesc, 1u);
+            mma_i8_lohi<kG>(d_tmem, a_lo + 4, a_lo + b_off + 4, desc_hi, idesc, 1u);
+            mma_i8_lohi<kG>(d_tmem, a_lo + 6, a_lo + b_off + 6, desc_hi, idesc, 1u);
+          }
+          acc = 1u;
+          commit_empty();
+          next_stage();
+        }
+        if (ok && full_kb < p.num_kb) {   // ragged last stage: 1..3 K steps
+          ok = wait_full();
+          if (ok) {
+            if (do_mma) {
+              for (int k = 0; k < p.last_ksteps; ++k) {
+                mma_i8_lohi<kG>(d_tmem, a_lo + 2 * k, a_lo + b_off + 2 * k, desc_hi, idesc, acc);
+                acc = 1u;
               }
             }
+            commit_empty();
+            next_stage();
           }
-          // Frees the stage (in both CTAs of a pair) once these MMAs have read it.
-          if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
-          else tc_commit_2cta(smem_u32(&ctrl->empty[stage]), 3);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (ok) {
           HY3D_TRACE_EVENT(1, tr, 3, it);
@@ -462,8 +487,15 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const uint32_t stage_buf = staging_base + static_cast<uint32_t>((warp - 2) * p.store_bufs) * kSlabBytes;
     const int acc_per_slab = geglu ? 2 * kSlabCols : kSlabCols;
     // The accumulator buffer is handed back to the leader's MMA warp (its own CTA or the peer).
+    // One arrival per warp: every lane's tcgen05.ld has completed (its own wait::ld), the
+    // warp converges, then lane 0 signals.  (An arrival per thread would put 512 serialised
+    // updates of one shared-memory word on the epilogue's critical path.)
     auto release_acc = [&](uint32_t bar) {
-      if (kG == 1 || leader) mbar_arrive(bar); else mbar_arrive_cluster(bar, 0);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (kG == 1 || leader) mbar_arrive(bar); else mbar_arrive_cluster(bar, 0);
+      }
     };
     bool ok = true;
     int it = 0;

@@ -98,7 +98,7 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
-      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kEpiThreads);
+      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kEpiWarps);   // one arrival per epilogue warp
     }
     ctrl->abort_flag = 0;
     fence_barrier_init();
@@ -330,9 +330,9 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           }
         }
       }
-      __syncwarp();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
     }
     if (p.tma_store && lane == 0) tma_store_wait_all<0>();
   }
