@@ -291,6 +291,36 @@ def run_ours(args):
             e0.record(); torch._int_mm(a8, b8.t()); e1.record(); torch.cuda.synchronize()
             best = min(best, e0.elapsed_time(e1))
         lib_int8 = round(2 * 8192 ** 3 / (best * 1e-3) / 1e12, 1)
+    except Exception:
+        pass
+    # The same square problem through this library's GEMM (int8 in, bf16 out with the fused
+    # rescale + bias epilogue): how close the kernel itself gets to the tensor roofline when the
+    # shape lets it (the sweep's UNet shapes are mostly bound by HBM or by their short K).
+    own_int8 = None
+    if not sparse:
+        try:
+            n8 = 8192
+            as8 = torch.rand(n8, device=dev) * 0.01
+            ws8 = torch.rand(n8, device=dev).bfloat16()
+            o8 = torch.empty((n8, n8), dtype=torch.bfloat16, device=dev)
+            cur = torch.cuda.current_stream().cuda_stream
+            best = 1e9
+            for i in range(6):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                st = lib.hy3d_gemm_w8a8_dense(a8.data_ptr(), b8.data_ptr(), as8.data_ptr(), ws8.data_ptr(), 1,
+                                              None, 1, o8.data_ptr(), 1, n8, n8, n8, 0, 0, 0, cur)
+                e1.record()
+                torch.cuda.synchronize()
+                if st != 0:
+                    raise RuntimeError(f"status {st}")
+                if i:
+                    best = min(best, e0.elapsed_time(e1))
+            own_int8 = round(2 * n8 ** 3 / (best * 1e-3) / 1e12, 1)
+            del as8, ws8, o8
+        except Exception:
+            pass
+    try:
         del a8, b8
     except Exception:
         pass
@@ -311,7 +341,7 @@ def run_ours(args):
                 "frac": round(gemm_tops / int8_peak, 4), "peak_source": peak_src,
                 "traffic": TRAFFIC_BYTES_PER_LAUNCH["sparse" if sparse else "dense"],
                 "traffic_source": "ncu dram bytes of one launch (profiles/), scaled by the sweep's algorithmic bytes",
-                "library_int8_gemm_8192_tops": lib_int8,
+                "library_int8_gemm_8192_tops": lib_int8, "own_gemm_8192_tops": own_int8,
                 "launches_per_step": len(SWEEP), "avg_launch_us": round(ms_gemm * 1e3 / len(SWEEP), 2),
                 "per_shape_bound": {"ms_per_step_at_bound": round(t_bound * 1e3, 4),
                                     "frac_of_bound": round(t_bound / (ms_gemm * 1e-3), 4),
