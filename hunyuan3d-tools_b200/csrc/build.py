@@ -56,25 +56,47 @@ def cuda_flags() -> list[str]:
 
 
 def _source_digest() -> str:
+    """Hash of the sources and of the flags that affect code generation.  Nothing in it
+    depends on where the tree lives, so a library built in one checkout is accepted as
+    up to date in a copy of that checkout elsewhere."""
     h = hashlib.sha256()
     for name in SOURCES + HEADERS:
         path = name if os.path.isabs(name) else os.path.join(_CSRC, name)
         with open(path, "rb") as f:
-            h.update(name.encode())
+            h.update(os.path.basename(name).encode())
             h.update(f.read())
-    h.update(" ".join(cuda_flags()).encode())
+    h.update(" ".join(fl for fl in cuda_flags() if fl != _REPO_INCLUDE).encode())
     return h.hexdigest()
 
 
+def _up_to_date(stamp: str, digest: str) -> bool:
+    if not (os.path.exists(LIB_PATH) and os.path.exists(stamp)):
+        return False
+    with open(stamp) as f:
+        return f.read().strip() == digest
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library if its sources changed; returns the path of the .so."""
+    """Compile the library if its sources changed; returns the path of the .so.  Several
+    processes may call this at once (one per GPU under torchrun): a file lock lets one of them
+    build while the others wait and then find the library up to date."""
     stamp = os.path.join(_BUILD_DIR, "digest.txt")
     digest = _source_digest()
-    if not force and os.path.exists(LIB_PATH) and os.path.exists(stamp):
-        with open(stamp) as f:
-            if f.read().strip() == digest:
-                return LIB_PATH
+    if not force and _up_to_date(stamp, digest):
+        return LIB_PATH
     os.makedirs(_BUILD_DIR, exist_ok=True)
+    import fcntl
+    with open(os.path.join(_BUILD_DIR, "build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and _up_to_date(stamp, digest):
+                return LIB_PATH
+            return _build_locked(stamp, digest, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(stamp: str, digest: str, verbose: bool) -> str:
     nvcc = _nvcc()
     flags = cuda_flags() + (["-Xptxas", "-v"] if verbose else [])
 
@@ -90,7 +112,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
         objs = list(pool.map(compile_one, SOURCES))
-    tmp = LIB_PATH + ".tmp"
+    tmp = LIB_PATH + f".tmp{os.getpid()}"
     cmd = [nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
            "-Xcompiler", "-fPIC"]
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -173,3 +173,21 @@ def test_oracle_is_not_imported_by_the_product():
             if f.endswith((".py", ".cu", ".cuh")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "import oracle" not in text and "from oracle" not in text, f
+
+
+def test_build_digest_does_not_depend_on_the_checkout_location(build_mod, tmp_path):
+    """A library built here must be accepted as up to date in a copy of the tree elsewhere
+    (one process per GPU would otherwise rebuild it concurrently on first use)."""
+    import importlib.util
+    import shutil
+    src_pkg = os.path.join(ROOT, "hunyuan3d-tools_b200", "csrc")
+    dst_pkg = tmp_path / "elsewhere" / "hunyuan3d-tools_b200" / "csrc"
+    dst_pkg.mkdir(parents=True)
+    for name in os.listdir(src_pkg):
+        if name.endswith((".cu", ".cuh", ".py")):
+            shutil.copy(os.path.join(src_pkg, name), dst_pkg / name)
+    shutil.copytree(os.path.join(ROOT, "include"), tmp_path / "elsewhere" / "include")
+    spec = importlib.util.spec_from_file_location("build_copy", dst_pkg / "build.py")
+    copy = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(copy)
+    assert copy._source_digest() == build_mod._source_digest()
