@@ -573,16 +573,26 @@ def run_unet(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=None,
+                    help="timed steps (default: 400 sweep passes, 50 UNet forwards, 5 CPU reference passes)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="dense_sweep", choices=["dense_sweep", "sparse_sweep", "unet", "multimesh"])
     ap.add_argument("--quant", default="mixed", choices=["mixed", "dense", "sparse", "none"])
-    ap.add_argument("--cpu-frac", type=float, default=1.0, help="row fraction of each shape timed on the CPU")
+    ap.add_argument("--cpu-frac", type=float, default=None,
+                    help="row fraction of each shape timed on the CPU (default: all rows, fewer when "
+                         "the requested number of reference passes would take more than ~2 minutes)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.steps is None:
+        args.steps = 5 if args.impl == "reference" else (50 if args.workload in ("unet", "multimesh") else 400)
+    if args.cpu_frac is None:
+        # One pass over all rows takes ~0.6 s on the host cores of the GPU box.
+        args.cpu_frac = 1.0
+        if args.impl == "reference":
+            args.cpu_frac = min(1.0, 120.0 / (0.6 * (args.steps + args.warmup)))
     if args.impl == "reference":
         run_reference(args)
     elif args.workload in ("unet", "multimesh"):
