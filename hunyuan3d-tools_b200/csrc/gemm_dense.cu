@@ -500,7 +500,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     bool ok = true;
     int it = 0;
     int cur_n0 = -1;
-    long long acc_ld = 0, acc_math = 0, acc_store = 0, acc_n = 0, acc_tile = 0, acc_wait = 0;
+    long long acc_tile = 0, acc_wait = 0;   // per-role cycle totals of a -DHY3D_TRACE build
     const bool scaled = p.out_dtype != HY3D_S32;
     // The activation scale of the NEXT tile's row is fetched one tile ahead, and the
     // per-column scales / bias are refilled only when the tile column changes (with the grid
@@ -677,8 +677,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       while (!*abort_flag && quantize_step<kBf16>(p, qw, lane)) { }
     }
     if (threadIdx.x == 64) {
-      HY3D_TRACE_RAW(0, acc_ld); HY3D_TRACE_RAW(1, acc_math); HY3D_TRACE_RAW(2, acc_store);
-      HY3D_TRACE_RAW(3, acc_n); HY3D_TRACE_RAW(4, acc_tile); HY3D_TRACE_RAW(5, acc_wait); HY3D_TRACE_RAW(6, it);
+      HY3D_TRACE_RAW(4, acc_tile); HY3D_TRACE_RAW(5, acc_wait); HY3D_TRACE_RAW(6, it);
     }
     // Global writes of the bulk stores must be complete before the CTA retires.
     if (p.tma_store && lane == 0) tma_store_wait_all<0>();
