@@ -272,11 +272,9 @@ int hy3d_mma_kat(const int8_t* a, const int8_t* b, const uint32_t* meta, int32_t
   }
   if (!meta) return HY3D_ERR_ARG;
   if (ksteps < 1 || ksteps > 2) return HY3D_ERR_SHAPE;
-  // The sparse GEMM computes out(M=tokens, N=weight rows); here the 128 compressed rows
-  // are the weight and the n rows of b are the tokens, so its output is D^T (n x 128).
-  // The caller-visible D is (128, n): ask for block_m = n and transpose on the host side
-  // of the ABI is not possible without allocation, so d is defined as (n, 128) row-major
-  // for the sparse case.
+  // The sparse GEMM computes out(M = tokens, N = weight rows); here the 128 compressed rows
+  // are the weight and the n rows of b are the tokens, so d receives D^T, (n, 128) row-major
+  // (as the header says); the binding transposes it back.
   const int64_t k = 64 * ksteps;
   return gemm_sparse24(b, nullptr, a, meta, 4 * ((k + 127) / 128), nullptr, HY3D_F32, nullptr,
                        HY3D_F32, d, HY3D_S32, n, 128, k, HY3D_EPI_LINEAR, n, s);

@@ -218,7 +218,10 @@ int hy3d_dequant_bias(const int32_t* acc, const float* act_scale,
  *   sparse == 0: D(128 x n) = A(128 x k) * B(n x k)^T, k = 32 * ksteps  (tcgen05.mma kind::i8)
  *   sparse == 1: A is 2:4 compressed (128 x k/2) with meta (128 x 4*ceil(k/128)) words,
  *                k = 64 * ksteps                                 (tcgen05.mma.sp kind::i8)
- * n: multiple of 16 in [16,256]; ksteps in [1,4] (dense) or [1,2] (sparse).  d: (128,n) int32.
+ * n: multiple of 16 in [16,256]; ksteps in [1,4] (dense) or [1,2] (sparse).
+ * d: int32, (128, n) row-major for the dense case; for the sparse case the tile is written
+ * transposed, (n, 128) row-major (the sparse kernel's accumulator is D[weight row, token] and
+ * its output is token-major).
  * Replaces: csrc/int8_sparse_tc.cu:350-408, 1587-1614 (test_mma_sp).
  */
 int hy3d_mma_kat(const int8_t* a, const int8_t* b, const uint32_t* meta,
