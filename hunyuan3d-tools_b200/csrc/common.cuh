@@ -336,6 +336,22 @@ __device__ __forceinline__ void mma_sp_i8_1cta(uint32_t d_tmem, uint64_t desc_a,
       ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(e_tmem), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// CTA-pair forms: A is 256 rows (128 per CTA), B is split by columns between the CTAs, each
+// CTA's metadata sits in its own tensor memory.
+__device__ __forceinline__ void mma_sp_i8_2cta(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b,
+                                               uint32_t e_tmem, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.sp.cta_group::2.kind::i8 [%0], %1, %2, [%3], %4, p;\n\t}"
+      ::"r"(d_tmem), "l"(desc_a), "l"(desc_b), "r"(e_tmem), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_cp_128x128b_2cta(uint32_t dst_tmem, uint64_t src_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(dst_tmem), "l"(src_desc)
+               : "memory");
+}
 // Shared memory -> tensor memory copy of 128 lanes x 128 bits (sparse metadata).
 __device__ __forceinline__ void tmem_cp_128x128b_1cta(uint32_t dst_tmem, uint64_t src_desc) {
   asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(dst_tmem), "l"(src_desc)

@@ -13,7 +13,14 @@
 // and tcgen05.mma issued by one thread execute in issue order, so one 8-column metadata slot
 // in tensor memory is enough.  Roles, accumulator double-buffering and bounded waits are as in
 // the dense kernel.
+//
+// CTA-pair variant (kG == 2, cta_group::2): a tile is 256 weight rows x block_t tokens; each
+// CTA stages its own 128 weight rows (A and E) and HALF of the token tile, so the activation
+// traffic into shared memory -- most of a stage -- is halved per CTA.  Loads are plain
+// cp.async.bulk.tensor ... .cta_group::2 crediting the leader's barrier (no multicast); the
+// leader issues tcgen05.cp / tcgen05.mma.sp for the pair and commits to both CTAs' barriers.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace hy3d {
 namespace sparse {
@@ -65,6 +72,7 @@ __device__ __forceinline__ void store_one(void* out, int out_dtype, int64_t idx,
     reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
 }
 
+template <int kG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_e,
                    const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_o,
@@ -77,7 +85,8 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     return;
   }
 
-  const uint32_t b_half = static_cast<uint32_t>(p.block_t) * 128u;   // one 128-byte-wide box of tokens
+  // One 128-byte-wide box of tokens; with a CTA pair each CTA stages half of the token tile.
+  const uint32_t b_half = static_cast<uint32_t>(p.block_t / kG) * 128u;
   const uint32_t b_bytes = 2u * b_half;
   const uint32_t stage_bytes = kABytes + kEBytes + b_bytes;
   const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
@@ -87,7 +96,13 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_tiles = p.w_tiles * p.t_tiles;
+  const int total_tiles = p.w_tiles * p.t_tiles;       // w_tiles counts 128*kG-row units
+  const uint32_t cta_rank = kG == 2 ? cluster_cta_rank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int first_tile = static_cast<int>(blockIdx.x) / kG;
+  const int tile_step = static_cast<int>(gridDim.x) / kG;
+  const int row_off = static_cast<int>(cta_rank) * kTileW;                 // this CTA's weight rows
+  const int tok_off = static_cast<int>(cta_rank) * (p.block_t / kG);       // this CTA's share of B
   const uint32_t tmem_cols = 512;
   const uint32_t e_col = static_cast<uint32_t>(2 * p.block_t);
 
@@ -98,7 +113,7 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
-      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kEpiWarps);   // one arrival per epilogue warp
+      mbar_init(smem_u32(&ctrl->tmem_empty[b]), kG * kEpiWarps);   // one arrival per epilogue warp
     }
     ctrl->abort_flag = 0;
     fence_barrier_init();
@@ -108,11 +123,17 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (p.tma_store) tma_prefetch_desc(&tm_o);
   }
   if (warp == 1) {
-    tmem_alloc_1cta(smem_u32(&ctrl->tmem_base), tmem_cols);
-    tmem_relinquish_1cta();
+    if (kG == 2) {
+      tmem_alloc_2cta(smem_u32(&ctrl->tmem_base), tmem_cols);
+      tmem_relinquish_2cta();
+    } else {
+      tmem_alloc_1cta(smem_u32(&ctrl->tmem_base), tmem_cols);
+      tmem_relinquish_1cta();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if (kG == 2) cluster_sync_all();   // the peer's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
   pdl_launch_dependents();
@@ -124,21 +145,32 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const int w0 = (tile % p.w_tiles) * kTileW;
-        const int t0 = (tile / p.w_tiles) * p.block_t;
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+        const int w0 = (tile % p.w_tiles) * (kTileW * kG) + row_off;
+        const int t0 = (tile / p.w_tiles) * p.block_t + tok_off;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
           if (!ok) break;
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_base + stage * stage_bytes;
           const uint32_t sb = sa + kABytes + kEBytes;
-          mbar_arrive_expect_tx(full, stage_bytes);
-          tma_load_2d(sa, &tm_w, full, kb * (kBlockK / 2), w0);
-          tma_load_2d(sa + kABytes, &tm_e, full, kb * (kBlockK / 8), w0);
-          tma_load_2d(sa + kABytes + kEBytes / 2, &tm_e, full, kb * (kBlockK / 8) + 16, w0);
-          tma_load_2d(sb, &tm_x, full, kb * kBlockK, t0);
-          tma_load_2d(sb + b_half, &tm_x, full, kb * kBlockK + 128, t0);
+          if (kG == 1) {
+            mbar_arrive_expect_tx(full, stage_bytes);
+            tma_load_2d(sa, &tm_w, full, kb * (kBlockK / 2), w0);
+            tma_load_2d(sa + kABytes, &tm_e, full, kb * (kBlockK / 8), w0);
+            tma_load_2d(sa + kABytes + kEBytes / 2, &tm_e, full, kb * (kBlockK / 8) + 16, w0);
+            tma_load_2d(sb, &tm_x, full, kb * kBlockK, t0);
+            tma_load_2d(sb + b_half, &tm_x, full, kb * kBlockK + 128, t0);
+          } else {
+            // Both CTAs credit their bytes to the leader's barrier; only the leader arrives.
+            const uint32_t full_leader = map_to_cta(full, 0);
+            if (leader) mbar_arrive_expect_tx(full, 2 * stage_bytes);
+            tma_load_2d_pair(sa, &tm_w, full_leader, kb * (kBlockK / 2), w0);
+            tma_load_2d_pair(sa + kABytes, &tm_e, full_leader, kb * (kBlockK / 8), w0);
+            tma_load_2d_pair(sa + kABytes + kEBytes / 2, &tm_e, full_leader, kb * (kBlockK / 8) + 16, w0);
+            tma_load_2d_pair(sb, &tm_x, full_leader, kb * kBlockK, t0);
+            tma_load_2d_pair(sb + b_half, &tm_x, full_leader, kb * kBlockK + 128, t0);
+          }
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
       }
@@ -146,15 +178,15 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer (one thread) ----------------
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_i8(kTileW, static_cast<uint32_t>(p.block_t), true);
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc_i8(kTileW * kG, static_cast<uint32_t>(p.block_t), true);
       const uint64_t desc128 = make_smem_desc(0, 1024, 128);
       const uint64_t desc_e = make_smem_desc(0, 128, 0);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
@@ -172,22 +204,38 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           const uint64_t db0 = desc128 | static_cast<uint64_t>((sb & 0x3FFFFu) >> 4);
           const uint64_t db1 = desc128 | static_cast<uint64_t>(((sb + b_half) & 0x3FFFFu) >> 4);
           // Metadata of the stage: two 128-lane x 128-bit copies = 8 columns = four K=64 steps.
-          tmem_cp_128x128b_1cta(tmem_base + e_col, desc_e | static_cast<uint64_t>((se & 0x3FFFFu) >> 4));
-          tmem_cp_128x128b_1cta(tmem_base + e_col + 4,
-                                desc_e | static_cast<uint64_t>(((se + kEBytes / 2) & 0x3FFFFu) >> 4));
+          const uint64_t de0 = desc_e | static_cast<uint64_t>((se & 0x3FFFFu) >> 4);
+          const uint64_t de1 = desc_e | static_cast<uint64_t>(((se + kEBytes / 2) & 0x3FFFFu) >> 4);
+          if (kG == 1) {
+            tmem_cp_128x128b_1cta(tmem_base + e_col, de0);
+            tmem_cp_128x128b_1cta(tmem_base + e_col + 4, de1);
+          } else {
+            tmem_cp_128x128b_2cta(tmem_base + e_col, de0);
+            tmem_cp_128x128b_2cta(tmem_base + e_col + 4, de1);
+          }
           const int nk = (kb == p.num_kb - 1) ? p.last_ksteps : 4;
           // Per K=64 instruction: 32 compressed bytes of A (+2 address units), 64 bytes of B
           // (+4; the second 128-byte box after two steps) and two metadata columns.
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            if (k < nk)
-              mma_sp_i8_1cta(d_tmem, da + 2 * k, (k < 2 ? db0 + 4 * k : db1 + 4 * (k - 2)),
-                             tmem_base + e_col + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (k < nk) {
+              const uint64_t dbk = k < 2 ? db0 + 4 * k : db1 + 4 * (k - 2);
+              if (kG == 1)
+                mma_sp_i8_1cta(d_tmem, da + 2 * k, dbk, tmem_base + e_col + 2 * k, idesc,
+                               (kb | k) != 0 ? 1u : 0u);
+              else
+                mma_sp_i8_2cta(d_tmem, da + 2 * k, dbk, tmem_base + e_col + 2 * k, idesc,
+                               (kb | k) != 0 ? 1u : 0u);
+            }
           }
-          tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
+          if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
+          else tc_commit_2cta(smem_u32(&ctrl->empty[stage]), 3);
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
-        if (ok) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
+        if (ok) {
+          if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
+          else tc_commit_2cta(smem_u32(&ctrl->tmem_full[buf]), 3);
+        }
       }
     }
     __syncwarp();
@@ -203,10 +251,10 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const uint32_t stage_buf = staging_base + static_cast<uint32_t>(warp - 2) * kSlabBytes;
     bool ok = true;
     int it = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int w0 = (tile % p.w_tiles) * kTileW;
+      const int w0 = (tile % p.w_tiles) * (kTileW * kG) + row_off;
       const int t0 = (tile / p.w_tiles) * p.block_t;
       const int n = w0 + row_in_tile;
       const bool n_ok = n < p.N;
@@ -332,7 +380,11 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+      if (lane == 0) {
+        // The accumulator buffer goes back to the leader's MMA warp (own CTA or the peer).
+        if (kG == 1 || leader) mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
+        else mbar_arrive_cluster(smem_u32(&ctrl->tmem_empty[buf]), 0);
+      }
     }
     if (p.tma_store && lane == 0) tma_store_wait_all<0>();
   }
@@ -345,9 +397,13 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     while (global_timer_ns() - t0 < 200000ull) { }
     __syncthreads();
   }
+  // Neither CTA of a pair may retire while the other can still touch its shared memory,
+  // barriers or tensor memory.
+  if (kG == 2) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc_1cta(tmem_base, tmem_cols);
+    if (kG == 2) tmem_dealloc_2cta(tmem_base, tmem_cols);
+    else tmem_dealloc_1cta(tmem_base, tmem_cols);
   }
 }
 
@@ -392,17 +448,30 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   }
   if (block_t < 16 || block_t > kMaxBlockT || (block_t & 15)) return HY3D_ERR_SHAPE;
 
+  // CTA pairs (256 weight rows sharing one token tile) halve each CTA's activation traffic
+  // into shared memory, which is what paces deep-K stages (measured: 8192^3 384 -> 273 us,
+  // M=3072 K=5120 N=1280 21.3 -> 15.7 us); on short K the per-tile hand-offs of a pair cost
+  // more than that saves, and a weight matrix that fills its last 256-row tile badly (N = 320)
+  // wastes the second CTA; launch-bound problems (M = 924) are faster with single CTAs.
+  int group = 1;
+  {
+    const int64_t padded = ((N + 2 * kTileW - 1) / (2 * kTileW)) * (2 * kTileW);
+    if (K >= 1024 && M >= 2048 && (block_t & 31) == 0 && padded * 4 <= N * 5) group = 2;
+    if (const char* e = getenv("HY3D_SPARSE_CTA_GROUP")) group = atoi(e) == 2 ? 2 : 1;
+    if (group == 2 && (block_t & 31)) group = 1;
+  }
+
   SparseArgs p;
   p.act_scale = act_scale; p.w_scale = w_scale; p.bias = bias; p.out = out;
   p.ws_dtype = ws_dtype; p.bias_dtype = bias_dtype; p.out_dtype = out_dtype; p.epilogue = epilogue;
   p.M = static_cast<int>(M); p.N = static_cast<int>(N); p.K = static_cast<int>(K);
   p.block_t = block_t;
-  p.w_tiles = static_cast<int>((N + kTileW - 1) / kTileW);
+  p.w_tiles = static_cast<int>((N + kTileW * group - 1) / (kTileW * group));
   p.t_tiles = static_cast<int>((M + block_t - 1) / block_t);
   p.num_kb = static_cast<int>(kblocks);
   const int k_last = static_cast<int>(K - (kblocks - 1) * kBlockK);
   p.last_ksteps = (k_last + 63) / 64;
-  const int stage_bytes = kABytes + kEBytes + block_t * kBlockK;
+  const int stage_bytes = kABytes + kEBytes + (block_t / group) * kBlockK;
   p.tma_store = (out_dtype != HY3D_S32 && epilogue != HY3D_EPI_GEGLU && block_t % kSlabTokens == 0) ? 1 : 0;
   const int fixed = static_cast<int>(sizeof(SparseCtrl)) + kEpiWarps * kSlabBytes;
   int stages = (kSmemLimit - fixed) / stage_bytes;
@@ -422,7 +491,7 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
                          static_cast<uint64_t>(meta_ld * 4), 16, kTileW, 0);
   if (rc != HY3D_OK) return rc;
   rc = encode_tmap_2d_u8(&tm_x, X, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
-                         static_cast<uint64_t>(K), 128, static_cast<uint32_t>(block_t), 128);
+                         static_cast<uint64_t>(K), 128, static_cast<uint32_t>(block_t / group), 128);
   if (rc != HY3D_OK) return rc;
 
   if (p.tma_store) {
@@ -434,28 +503,37 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
     tm_o = tm_x;   // unused by the kernel
   }
 
-  static bool attr_set[64] = {};
+  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                            const CUtensorMap, const SparseArgs);
+  const KernelFn kernel = group == 2 ? gemm_sparse_kernel<2> : gemm_sparse_kernel<1>;
+  static bool attr_set[64][2] = {};
   const int dev = current_device();
   if (dev < 0 || dev >= 64) return HY3D_ERR_CUDA;
-  if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm_sparse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemLimit) != cudaSuccess)
+  if (!attr_set[dev][group - 1]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
+        cudaSuccess)
       return HY3D_ERR_CUDA;
-    attr_set[dev] = true;
+    attr_set[dev][group - 1] = true;
   }
   const int sms = device_sm_count();
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.w_tiles * p.t_tiles;
-  const int grid = total_tiles < sms ? total_tiles : sms;
+  const int max_clusters = sms / group;
+  const int clusters = total_tiles < max_clusters ? total_tiles : max_clusters;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.gridDim = dim3(static_cast<unsigned>(group * clusters));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1] = {pdl_attribute()};
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(group);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1] = pdl_attribute();
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm_sparse_kernel, tm_w, tm_e, tm_x, tm_o, p) != cudaSuccess) {
+  cfg.numAttrs = 2;
+  if (cudaLaunchKernelEx(&cfg, kernel, tm_w, tm_e, tm_x, tm_o, p) != cudaSuccess) {
     cudaGetLastError();
     return HY3D_ERR_CUDA;
   }
