@@ -236,6 +236,8 @@ def test_sparse_tile_known_answer_from_reference_tests(sp, golden):
     (4096, 320, 320, 0), (12288, 2560, 640, 240), (3, 1280, 1280, 0), (64, 640, 5120, 0),
     (257, 1536, 4608, 0), (500, 64, 16, 0), (2772, 1024, 320, 128), (1, 64, 16, 0),
     (700, 5120, 1280, 224),
+    # deep K, M >= 2048: the CTA-pair variant (256 weight rows per tile), full and ragged tiles
+    (2304, 1024, 512, 0), (2100, 2560, 640, 0), (3000, 1280, 1296, 192), (2048, 5120, 1280, 64),
 ])
 def test_sparse_accumulators_bit_exact(sp, M, K, N, bt):
     X, W = _rand_i8((M, K), M + K), _rand_i8((N, K), N + K + 5)
@@ -244,6 +246,24 @@ def test_sparse_accumulators_bit_exact(sp, M, K, N, bt):
                               force_tile=bt)
     co, no = O.prune_compress(W)
     assert torch.equal(acc.cpu(), O.int32_matmul(X, O.expand_24(co, no)))
+
+
+@pytest.mark.parametrize("mode,code", [("linear", 0), ("gelu", 1), ("geglu", 2)])
+def test_sparse_pair_variant_epilogues(sp, mode, code):
+    """Scaled outputs of the CTA-pair variant (chosen for K >= 1024, M >= 2048)."""
+    M, K, N = 2500, 1280, 768
+    A, B = _rand_i8((M, K), 31), _rand_i8((N, K), 32)
+    g = torch.Generator().manual_seed(33)
+    a_s = torch.rand(M, generator=g) * 0.05 + 1e-3
+    w_s = (torch.rand(N, generator=g) * 1e-3 + 1e-5).bfloat16()
+    bias = (torch.randn(N, generator=g) * 0.1).bfloat16()
+    comp, meta = sp.sparse_prune_and_pack(B.to(DEV))
+    y = sp.sparse_int8_gemm(A.to(DEV), a_s.to(DEV), comp, meta, w_s.to(DEV), bias.to(DEV),
+                            out_dtype=torch.bfloat16, epilogue=code)
+    co, no = O.prune_compress(B)
+    ref = O.epilogue(O.int32_matmul(A, O.expand_24(co, no)), a_s, w_s, bias, torch.bfloat16, mode)
+    assert y.shape == ref.shape
+    assert O.rel_l2(y, ref) < 2e-3
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
