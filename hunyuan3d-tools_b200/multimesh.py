@@ -132,7 +132,7 @@ def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed:
         stats = qu.quantize_model_sparse(unet, verbose=verbose)
     elif quant != "none":
         raise ValueError(f"unknown quant mode {quant!r}")
-    if fuse_geglu and quant in ("mixed", "dense"):
+    if fuse_geglu and quant in ("mixed", "dense", "sparse"):
         stats["geglu_fused"] = fuse_geglu_layers(unet)
     if fuse_qkv and quant != "none":
         stats["qkv_layers_removed"] = fuse_qkv_layers(unet)

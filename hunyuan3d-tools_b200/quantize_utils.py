@@ -238,17 +238,24 @@ class Int8Linear(nn.Module):
     def interleave_geglu_rows(self) -> "Int8Linear":
         """Re-orders a GEGLU up-projection ([value(H) | gate(H)] output rows) into blocks of
         16 value rows followed by their 16 gate rows and switches the layer to the fused
-        ``value * gelu(gate)`` epilogue; the layer then returns H columns.  Dense mode only
-        (a sparse layer must be interleaved before pruning)."""
-        if self.mode != "tc":
-            raise RuntimeError("interleave_geglu_rows applies to dense layers")
+        ``value * gelu(gate)`` epilogue; the layer then returns H columns.  Works for dense and
+        2:4-sparse layers alike: pruning acts along K inside a row, so permuting whole rows of
+        the compressed weights and their metadata commutes with it."""
+        if self.mode not in ("tc", "sparse"):
+            raise RuntimeError("interleave_geglu_rows applies to INT8 layers")
+        if self.epilogue != "linear":
+            raise RuntimeError("the layer already has a fused epilogue")
         n2 = self.out_features
         if n2 % 32:
             raise RuntimeError("GEGLU fusion needs out_features % 32 == 0")
         h = n2 // 2
-        idx = torch.arange(h, device=self.weight_int8_nk.device).view(h // 16, 16)
+        idx = torch.arange(h, device=self.weight_scale.device).view(h // 16, 16)
         perm = torch.stack([idx, idx + h], dim=1).reshape(-1)
-        self.weight_int8_nk = self.weight_int8_nk[perm].contiguous()
+        if self.mode == "sparse":
+            self.weight_sparse_comp = self.weight_sparse_comp[perm].contiguous()
+            self.weight_sparse_meta = self.weight_sparse_meta[perm].contiguous()
+        else:
+            self.weight_int8_nk = self.weight_int8_nk[perm].contiguous()
         self.weight_scale = self.weight_scale[perm].contiguous()
         if self.bias is not None:
             self.bias = self.bias[perm].contiguous()

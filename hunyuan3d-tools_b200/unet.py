@@ -247,13 +247,13 @@ class UNetSD21MV(nn.Module):
 
 
 def fuse_geglu_layers(model: nn.Module) -> int:
-    """Switches every dense ``Int8Linear`` GEGLU up-projection to the fused
+    """Switches every ``Int8Linear`` GEGLU up-projection (dense or 2:4 sparse) to the fused
     ``value * gelu(gate)`` epilogue (rows interleaved offline).  Returns the number fused."""
     from .quantize_utils import Int8Linear
     n = 0
     for m in model.modules():
-        if isinstance(m, GEGLUFeedForward) and isinstance(m.proj, Int8Linear) and m.proj.mode == "tc" \
-                and m.proj.epilogue == "linear":
+        if isinstance(m, GEGLUFeedForward) and isinstance(m.proj, Int8Linear) \
+                and m.proj.mode in ("tc", "sparse") and m.proj.epilogue == "linear":
             m.proj.interleave_geglu_rows()
             n += 1
     return n

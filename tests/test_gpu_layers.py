@@ -128,6 +128,23 @@ def test_geglu_fused_layer(qu):
     assert O.rel_l2(y, v * torch.nn.functional.gelu(g)) < 1e-2
 
 
+@pytest.mark.parametrize("M", [1000, 3072])
+def test_geglu_fused_sparse_layer(qu, M):
+    """Row interleaving commutes with 2:4 pruning (which acts along K inside a row), so a
+    sparse up-projection can be switched to the fused GEGLU epilogue after conversion; M = 3072
+    takes the CTA-pair variant of the sparse kernel."""
+    torch.manual_seed(5)
+    lin = nn.Linear(1280, 2560).to(DEV).bfloat16()
+    x = torch.randn(M, 1280, device=DEV, dtype=torch.bfloat16)
+    plain = qu.Int8Linear.from_linear_sparse(lin)
+    fused = qu.Int8Linear.from_linear_sparse(lin).interleave_geglu_rows()
+    assert fused.mode == "sparse" and fused.epilogue == "geglu"
+    v, g = plain(x).float().chunk(2, dim=-1)
+    y = fused(x)
+    assert y.shape == (M, 1280)
+    assert O.rel_l2(y, v * torch.nn.functional.gelu(g)) < 1e-2
+
+
 def test_mixed_model_surgery(qu):
     torch.manual_seed(4)
     model = nn.Sequential(nn.Linear(320, 1280), nn.Linear(1280, 320), nn.Linear(320, 64)).to(DEV).half()
