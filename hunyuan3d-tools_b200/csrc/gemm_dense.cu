@@ -58,6 +58,7 @@ struct DenseArgs {
   int M, N, K;
   int block_n, stages, acc_cols, tma_store, store_bufs;
   int m_tiles, n_tiles, num_kb, last_ksteps, n_fastest;
+  int atoms;   // 128-byte K blocks per pipeline stage (1 or 2)
   int debug;   // diagnostic switches (HY3D_DEBUG): 1 no TMA loads, 2 no epilogue work, 4 no MMA
   // Fused activation quantiser (all unused when the kernel is not instantiated with kFused).
   const uint16_t* qx;   // fp16 / bf16 activations (M, K), row pitch q_ldx elements
@@ -300,7 +301,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const uint32_t a_bytes = kTileM * kBlockKBytes;
   // With a CTA pair (kG == 2) each CTA stages its own 128 rows of A and half of the B tile.
   const uint32_t b_bytes = static_cast<uint32_t>(p.block_n / kG) * kBlockKBytes;
-  const uint32_t stage_bytes = a_bytes + b_bytes;
+  // A stage holds p.atoms 128-byte-wide K blocks of each operand: [A0][A1..][B0][B1..].
+  const uint32_t stage_bytes = static_cast<uint32_t>(p.atoms) * (a_bytes + b_bytes);
   const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
   DenseCtrl* ctrl = reinterpret_cast<DenseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes +
                                                  kEpiWarps * p.store_bufs * kSlabBytes);
@@ -379,14 +381,20 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             if (leader) mbar_arrive(full);
           } else if (kG == 1) {
             mbar_arrive_expect_tx(full, stage_bytes);
-            tma_load_2d(sa, &tm_a, full, kb * kBlockKBytes, m0);
-            tma_load_2d(sa + a_bytes, &tm_b, full, kb * kBlockKBytes, n0);
+            for (int a = 0; a < p.atoms; ++a) {
+              const int kx = (kb * p.atoms + a) * kBlockKBytes;   // past K: zero-filled
+              tma_load_2d(sa + a * a_bytes, &tm_a, full, kx, m0);
+              tma_load_2d(sa + p.atoms * a_bytes + a * b_bytes, &tm_b, full, kx, n0);
+            }
           } else {
             // Both CTAs credit their bytes to the leader's barrier; only the leader arrives.
             const uint32_t full_leader = map_to_cta(full, 0);
             if (leader) mbar_arrive_expect_tx(full, 2 * stage_bytes);
-            tma_load_2d_pair(sa, &tm_a, full_leader, kb * kBlockKBytes, m0);
-            tma_load_2d_pair(sa + a_bytes, &tm_b, full_leader, kb * kBlockKBytes, n0);
+            for (int a = 0; a < p.atoms; ++a) {
+              const int kx = (kb * p.atoms + a) * kBlockKBytes;
+              tma_load_2d_pair(sa + a * a_bytes, &tm_a, full_leader, kx, m0);
+              tma_load_2d_pair(sa + p.atoms * a_bytes + a * b_bytes, &tm_b, full_leader, kx, n0);
+            }
           }
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
@@ -409,9 +417,11 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t lo_const = static_cast<uint32_t>(desc_const);
       const uint32_t a_lo0 = lo_const | ((smem_base & 0x3FFFFu) >> 4);
       const uint32_t stage_step = stage_bytes >> 4;
-      const uint32_t b_off = a_bytes >> 4;
+      const uint32_t a_atom = a_bytes >> 4, b_atom = b_bytes >> 4;
+      const uint32_t b_off = static_cast<uint32_t>(p.atoms) * a_atom;
       const bool do_mma = !(p.debug & 4);
-      const int full_kb = p.last_ksteps == 4 ? p.num_kb : p.num_kb - 1;   // stages with 4 K steps
+      // stages with the full 4 K steps per 128-byte block
+      const int full_kb = p.last_ksteps == 4 * p.atoms ? p.num_kb : p.num_kb - 1;
       int stage = 0;
       uint32_t phase = 0;
       uint32_t a_lo = a_lo0;
@@ -445,21 +455,29 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           ok = wait_full();
           if (!ok) break;
           if (do_mma) {
-            mma_i8_lohi<kG>(d_tmem, a_lo, a_lo + b_off, desc_hi, idesc, acc);
-            mma_i8_lohi<kG>(d_tmem, a_lo + 2, a_lo + b_off + 2, desc_hi, idesc, 1u);
-            mma_i8_lohi<kG>(d_tmem, a_lo + 4, a_lo + b_off + 4, desc_hi, idesc, 1u);
-            mma_i8_lohi<kG>(d_tmem, a_lo + 6, a_lo + b_off + 6, desc_hi, idesc, 1u);
+            uint32_t xa = a_lo, xb = a_lo + b_off;
+            for (int a = 0; a < p.atoms; ++a) {
+              mma_i8_lohi<kG>(d_tmem, xa, xb, desc_hi, idesc, acc);
+              mma_i8_lohi<kG>(d_tmem, xa + 2, xb + 2, desc_hi, idesc, 1u);
+              mma_i8_lohi<kG>(d_tmem, xa + 4, xb + 4, desc_hi, idesc, 1u);
+              mma_i8_lohi<kG>(d_tmem, xa + 6, xb + 6, desc_hi, idesc, 1u);
+              acc = 1u;
+              xa += a_atom;
+              xb += b_atom;
+            }
           }
           acc = 1u;
           commit_empty();
           next_stage();
         }
-        if (ok && full_kb < p.num_kb) {   // ragged last stage: 1..3 K steps
+        if (ok && full_kb < p.num_kb) {   // ragged last stage: fewer K steps
           ok = wait_full();
           if (ok) {
             if (do_mma) {
               for (int k = 0; k < p.last_ksteps; ++k) {
-                mma_i8_lohi<kG>(d_tmem, a_lo + 2 * k, a_lo + b_off + 2 * k, desc_hi, idesc, acc);
+                const uint32_t at = static_cast<uint32_t>(k >> 2), kk = static_cast<uint32_t>(k & 3);
+                mma_i8_lohi<kG>(d_tmem, a_lo + at * a_atom + 2 * kk,
+                                a_lo + b_off + at * b_atom + 2 * kk, desc_hi, idesc, acc);
                 acc = 1u;
               }
             }
@@ -775,11 +793,13 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   int group = cta_group;
   if (group == 0) {
     // CTA pairs halve the B traffic into shared memory, which is what bounds the tensor pipe
-    // on deep-K problems (measured: 8192^3 2768 vs 2332 TOPS); they pay off once the grid
-    // holds several rounds of 256-row tile pairs, and cost a little on short-K or small grids.
+    // on deep-K problems (measured: 8192^3 2768 vs 2332 TOPS); with K >= 2048 they pay off
+    // as soon as most SM pairs have a tile, with K >= 1024 once the grid holds several rounds
+    // of 256-row tile pairs; on shorter K the per-tile hand-offs of a pair cost more.
     const int sms = device_sm_count() > 0 ? device_sm_count() : 148;
     const int64_t pair_tiles = ((M + 2 * kTileM - 1) / (2 * kTileM)) * ((N + block_n - 1) / block_n);
-    group = (!fused && K >= 1024 && (block_n & 31) == 0 && pair_tiles >= 4 * (sms / 2)) ? 2 : 1;
+    const int64_t min_pair_tiles = K >= 2048 ? (sms / 2) * 4 / 5 : 4 * (sms / 2);
+    group = (!fused && K >= 1024 && (block_n & 31) == 0 && pair_tiles >= min_pair_tiles) ? 2 : 1;
     if (const char* e = getenv("HY3D_CTA_GROUP")) group = atoi(e) == 2 ? 2 : 1;
   }
   if (fused) {
@@ -803,18 +823,25 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   p.acc_cols = acc_cols;
   p.m_tiles = static_cast<int>((M + kTileM * group - 1) / (kTileM * group));
   p.n_tiles = static_cast<int>((N + block_n - 1) / block_n);
-  p.num_kb = static_cast<int>((K + kBlockKBytes - 1) / kBlockKBytes);
-  const int k_last = static_cast<int>(K - static_cast<int64_t>(p.num_kb - 1) * kBlockKBytes);
+  // Deep stages (two 128-byte K blocks, eight MMAs per barrier round trip) for CTA pairs on
+  // deep K: a pair's per-stage hand-off crosses the cluster, and halving the number of
+  // hand-offs is what lets pairs profit from their smaller shared-memory traffic.
+  int atoms = (group == 2 && K >= 1024) ? 2 : 1;
+  if (const char* e = getenv("HY3D_ATOMS")) atoms = atoi(e) == 2 ? 2 : 1;
+  p.atoms = atoms;
+  const int stage_k = kBlockKBytes * atoms;
+  p.num_kb = static_cast<int>((K + stage_k - 1) / stage_k);
+  const int k_last = static_cast<int>(K - static_cast<int64_t>(p.num_kb - 1) * stage_k);
   p.last_ksteps = (k_last + 31) / 32;
   p.tma_store = (out_dtype != HY3D_S32 && block_n % (geglu ? 2 * kSlabCols : kSlabCols) == 0) ? 1 : 0;
-  const int stage_bytes = kTileM * kBlockKBytes + (block_n / group) * kBlockKBytes;
-  // Two staging buffers per epilogue warp unless that costs a pipeline stage below four.
+  const int stage_bytes = atoms * (kTileM * kBlockKBytes + (block_n / group) * kBlockKBytes);
+  // Two staging buffers per epilogue warp unless that costs one of fewer than four pipeline stages.
   int store_bufs = 2;
   {
     const int fixed2 = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * 2 * kSlabBytes;
     const int fixed1 = fixed2 - kEpiWarps * kSlabBytes;
-    if ((kSmemLimit - fixed2) / stage_bytes < 4 && (kSmemLimit - fixed1) / stage_bytes >= 4)
-      store_bufs = 1;
+    const int stages2 = (kSmemLimit - fixed2) / stage_bytes, stages1 = (kSmemLimit - fixed1) / stage_bytes;
+    if (stages2 < 4 && stages1 > stages2) store_bufs = 1;
     if (const char* e = getenv("HY3D_STORE_BUFS")) store_bufs = atoi(e) == 1 ? 1 : 2;
   }
   p.store_bufs = store_bufs;
