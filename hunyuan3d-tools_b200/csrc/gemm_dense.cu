@@ -286,7 +286,7 @@ __device__ __forceinline__ void slab_store(const uint32_t (&packed)[16], uint32_
   }
 }
 
-template <bool kBf16, int kEpi, int kG, bool kFused>
+template <bool kBf16, int kEpi, int kG, bool kFused, int kAtoms>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_o, const DenseArgs p) {
@@ -301,8 +301,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const uint32_t a_bytes = kTileM * kBlockKBytes;
   // With a CTA pair (kG == 2) each CTA stages its own 128 rows of A and half of the B tile.
   const uint32_t b_bytes = static_cast<uint32_t>(p.block_n / kG) * kBlockKBytes;
-  // A stage holds p.atoms 128-byte-wide K blocks of each operand: [A0][A1..][B0][B1..].
-  const uint32_t stage_bytes = static_cast<uint32_t>(p.atoms) * (a_bytes + b_bytes);
+  // A stage holds kAtoms 128-byte-wide K blocks of each operand: [A0][A1..][B0][B1..].
+  const uint32_t stage_bytes = static_cast<uint32_t>(kAtoms) * (a_bytes + b_bytes);
   const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
   DenseCtrl* ctrl = reinterpret_cast<DenseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes +
                                                  kEpiWarps * p.store_bufs * kSlabBytes);
@@ -381,19 +381,21 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             if (leader) mbar_arrive(full);
           } else if (kG == 1) {
             mbar_arrive_expect_tx(full, stage_bytes);
-            for (int a = 0; a < p.atoms; ++a) {
-              const int kx = (kb * p.atoms + a) * kBlockKBytes;   // past K: zero-filled
+#pragma unroll
+            for (int a = 0; a < kAtoms; ++a) {
+              const int kx = (kb * kAtoms + a) * kBlockKBytes;   // past K: zero-filled
               tma_load_2d(sa + a * a_bytes, &tm_a, full, kx, m0);
-              tma_load_2d(sa + p.atoms * a_bytes + a * b_bytes, &tm_b, full, kx, n0);
+              tma_load_2d(sa + kAtoms * a_bytes + a * b_bytes, &tm_b, full, kx, n0);
             }
           } else {
             // Both CTAs credit their bytes to the leader's barrier; only the leader arrives.
             const uint32_t full_leader = map_to_cta(full, 0);
             if (leader) mbar_arrive_expect_tx(full, 2 * stage_bytes);
-            for (int a = 0; a < p.atoms; ++a) {
-              const int kx = (kb * p.atoms + a) * kBlockKBytes;
+#pragma unroll
+            for (int a = 0; a < kAtoms; ++a) {
+              const int kx = (kb * kAtoms + a) * kBlockKBytes;
               tma_load_2d_pair(sa + a * a_bytes, &tm_a, full_leader, kx, m0);
-              tma_load_2d_pair(sa + p.atoms * a_bytes + a * b_bytes, &tm_b, full_leader, kx, n0);
+              tma_load_2d_pair(sa + kAtoms * a_bytes + a * b_bytes, &tm_b, full_leader, kx, n0);
             }
           }
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
@@ -418,10 +420,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t a_lo0 = lo_const | ((smem_base & 0x3FFFFu) >> 4);
       const uint32_t stage_step = stage_bytes >> 4;
       const uint32_t a_atom = a_bytes >> 4, b_atom = b_bytes >> 4;
-      const uint32_t b_off = static_cast<uint32_t>(p.atoms) * a_atom;
+      const uint32_t b_off = static_cast<uint32_t>(kAtoms) * a_atom;
       const bool do_mma = !(p.debug & 4);
       // stages with the full 4 K steps per 128-byte block
-      const int full_kb = p.last_ksteps == 4 * p.atoms ? p.num_kb : p.num_kb - 1;
+      const int full_kb = p.last_ksteps == 4 * kAtoms ? p.num_kb : p.num_kb - 1;
       int stage = 0;
       uint32_t phase = 0;
       uint32_t a_lo = a_lo0;
@@ -456,7 +458,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if (!ok) break;
           if (do_mma) {
             uint32_t xa = a_lo, xb = a_lo + b_off;
-            for (int a = 0; a < p.atoms; ++a) {
+#pragma unroll
+            for (int a = 0; a < kAtoms; ++a) {
               mma_i8_lohi<kG>(d_tmem, xa, xb, desc_hi, idesc, acc);
               mma_i8_lohi<kG>(d_tmem, xa + 2, xb + 2, desc_hi, idesc, 1u);
               mma_i8_lohi<kG>(d_tmem, xa + 4, xb + 4, desc_hi, idesc, 1u);
@@ -826,8 +829,7 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   // Deep stages (two 128-byte K blocks, eight MMAs per barrier round trip) for CTA pairs on
   // deep K: a pair's per-stage hand-off crosses the cluster, and halving the number of
   // hand-offs is what lets pairs profit from their smaller shared-memory traffic.
-  int atoms = (group == 2 && K >= 1024) ? 2 : 1;
-  if (const char* e = getenv("HY3D_ATOMS")) atoms = atoi(e) == 2 ? 2 : 1;
+  const int atoms = (group == 2 && K >= 1024) ? 2 : 1;
   p.atoms = atoms;
   const int stage_k = kBlockKBytes * atoms;
   p.num_kb = static_cast<int>((K + stage_k - 1) / stage_k);
@@ -889,25 +891,21 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   }
 
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const DenseArgs);
-  // [0]: one CTA per tile, [1]: CTA pairs, [2]: one CTA per tile with the quantiser fused in.
-  static const KernelFn kernels[3][2][3] = {
-      {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, 1, false>, gemm_dense_kernel<false, HY3D_EPI_GELU, 1, false>,
-        gemm_dense_kernel<false, HY3D_EPI_GEGLU, 1, false>},
-       {gemm_dense_kernel<true, HY3D_EPI_LINEAR, 1, false>, gemm_dense_kernel<true, HY3D_EPI_GELU, 1, false>,
-        gemm_dense_kernel<true, HY3D_EPI_GEGLU, 1, false>}},
-      {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, 2, false>, gemm_dense_kernel<false, HY3D_EPI_GELU, 2, false>,
-        gemm_dense_kernel<false, HY3D_EPI_GEGLU, 2, false>},
-       {gemm_dense_kernel<true, HY3D_EPI_LINEAR, 2, false>, gemm_dense_kernel<true, HY3D_EPI_GELU, 2, false>,
-        gemm_dense_kernel<true, HY3D_EPI_GEGLU, 2, false>}},
-      {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, 1, true>, gemm_dense_kernel<false, HY3D_EPI_GELU, 1, true>,
-        gemm_dense_kernel<false, HY3D_EPI_GEGLU, 1, true>},
-       {gemm_dense_kernel<true, HY3D_EPI_LINEAR, 1, true>, gemm_dense_kernel<true, HY3D_EPI_GELU, 1, true>,
-        gemm_dense_kernel<true, HY3D_EPI_GEGLU, 1, true>}}};
+  // [0]: one CTA per tile, [1]: CTA pairs, [2]: one CTA per tile with the quantiser fused in,
+  // [3]: CTA pairs with deep (two-block) stages.
+#define HY3D_DENSE_ROW(G, F, A)                                                              \
+  {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, G, F, A>, gemm_dense_kernel<false, HY3D_EPI_GELU, G, F, A>, \
+    gemm_dense_kernel<false, HY3D_EPI_GEGLU, G, F, A>},                                        \
+   {gemm_dense_kernel<true, HY3D_EPI_LINEAR, G, F, A>, gemm_dense_kernel<true, HY3D_EPI_GELU, G, F, A>,   \
+    gemm_dense_kernel<true, HY3D_EPI_GEGLU, G, F, A>}}
+  static const KernelFn kernels[4][2][3] = {HY3D_DENSE_ROW(1, false, 1), HY3D_DENSE_ROW(2, false, 1),
+                                            HY3D_DENSE_ROW(1, true, 1), HY3D_DENSE_ROW(2, false, 2)};
+#undef HY3D_DENSE_ROW
   // Raw int32 output runs the direct-store path of the <false, LINEAR> instance.
   const int ki = out_dtype == HY3D_BF16 ? 1 : 0;
-  const int variant = fused ? 2 : group - 1;
+  const int variant = fused ? 2 : (group == 2 && atoms == 2 ? 3 : group - 1);
   const KernelFn kernel = kernels[variant][ki][epilogue];
-  static bool attr_set[64][3][2][3] = {};
+  static bool attr_set[64][4][2][3] = {};
   const int dev = current_device();
   if (dev < 0 || dev >= 64) return HY3D_ERR_CUDA;
   if (!attr_set[dev][variant][ki][epilogue]) {

@@ -113,6 +113,22 @@ def test_dense_accumulators_bit_exact(tc, M, K, N, bn):
     assert torch.equal(acc.cpu(), O.int32_matmul(A, B))
 
 
+@pytest.mark.parametrize("M,K,N,bn", [
+    (2600, 2064, 512, 0),     # K = 8 deep stages + a 16-element tail; ragged last row tile
+    (300, 1024, 256, 256),    # exactly four deep stages, second CTA's rows half empty
+    (1000, 1104, 320, 160),   # tail of 80: three K steps of the first block
+    (513, 5120, 1280, 224),   # ragged tile columns (1280 = 5 x 224 + 160)
+    (256, 320, 640, 128),     # short K with pairs: single 128-byte blocks per stage
+])
+def test_dense_cta_pairs_bit_exact(tc, M, K, N, bn):
+    """The CTA-pair variant (cta_group = 2: 256-row tiles; deep two-block stages from K = 1024)."""
+    A, B = _rand_i8((M, K), M + K + 2), _rand_i8((N, K), N + K + 3)
+    acc = tc.int8_gemm_tc(A.to(DEV), B.to(DEV), None, None, None, out_dtype=torch.int32,
+                          cta_group=2, block_n=bn)
+    assert torch.equal(acc.cpu(), O.int32_matmul(A, B))
+    assert tc.device_status() == 0
+
+
 def test_dense_extreme_values_no_overflow(tc):
     """|acc| reaches 128*128*K: the int32 accumulators must not saturate or wrap."""
     M, K, N = 128, 5120, 64
