@@ -35,9 +35,10 @@ SIGNATURES = {
     "hy3d_linear_w8a8_dense": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64,
                                c_int, c_int, c_int, c_void_p],
-    "hy3d_linear_w8a8_dense_fused": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int64,
-                                     c_int64, c_int64, c_int, c_int, c_void_p],
+    "hy3d_linear_w8a8_dense_fused": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int,
+                                     c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64,
+                                     c_int, c_int, c_void_p],
+    "hy3d_linear_path": [c_int64, c_int64, c_int64, c_int],
     "hy3d_linear_w8a8_dense_static": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p,
                                       c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_int,
                                       c_void_p],
@@ -53,11 +54,25 @@ SIGNATURES = {
                           c_int64, c_int64, c_void_p],
     "hy3d_mma_kat": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "hy3d_last_device_status": [c_void_p],
+    "hy3d_stream_status": [c_void_p],
+    "hy3d_set_wait_limit_ns": [ctypes.c_ulonglong],
+    "hy3d_wait_selftest": [c_void_p],
     "hy3d_version": [],
 }
 
+# The argument lists above belong to this ABI version of the library (hy3d_version()).
+ABI_VERSION = 200
+
 
 def configure(lib: ctypes.CDLL) -> ctypes.CDLL:
+    """Sets argument / result types and refuses a library built for another ABI version: a
+    stale .so driven with newer argument lists would hand wrong pointers to the kernels."""
+    lib.hy3d_version.argtypes = []
+    lib.hy3d_version.restype = c_int
+    found = lib.hy3d_version()
+    if found != ABI_VERSION:
+        raise RuntimeError(f"libhy3d_int8.so has ABI version {found}, this binding needs "
+                           f"{ABI_VERSION}; rebuild it with `python csrc/build.py`")
     for name, argtypes in SIGNATURES.items():
         fn = getattr(lib, name)
         fn.argtypes = argtypes
@@ -65,10 +80,10 @@ def configure(lib: ctypes.CDLL) -> ctypes.CDLL:
     for name in ("hy3d_static_scratch_max_bytes", "hy3d_static_scratch_max_rows"):
         getattr(lib, name).restype = c_int64
         getattr(lib, name).argtypes = []
-    lib.hy3d_fused_sync_bytes.restype = ctypes.c_size_t
-    lib.hy3d_fused_sync_bytes.argtypes = [c_int64]
     lib.hy3d_arch.restype = ctypes.c_char_p
     lib.hy3d_arch.argtypes = []
+    lib.hy3d_source_digest.restype = ctypes.c_char_p
+    lib.hy3d_source_digest.argtypes = []
     lib.hy3d_status_string.restype = ctypes.c_char_p
     lib.hy3d_status_string.argtypes = [c_int]
     return lib
@@ -117,6 +132,17 @@ class _Base:
         v = c_int(0)
         self._check(self._lib.hy3d_last_device_status(ctypes.byref(v)), "hy3d_last_device_status")
         return v.value
+
+    def check_stream(self, device=None):
+        """Waits for the current stream and raises if a kernel gave up one of its bounded
+        waits (its output is then undefined); the error word is cleared by the raise."""
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        with torch.cuda.device(dev):
+            rc = self._lib.hy3d_stream_status(torch.cuda.current_stream(dev).cuda_stream)
+            if rc != 0:
+                code = self.device_status() if rc == 5 else 0
+                msg = self._lib.hy3d_status_string(rc).decode()
+                raise RuntimeError(f"{msg} (status {rc}, device code {code})")
 
     # -- shared kernels ------------------------------------------------------------------
     def _quantize(self, x: torch.Tensor):
@@ -203,55 +229,37 @@ class TcGemmModule(_Base):
                 "hy3d_gemm_w8a8_dense")
         return out
 
-    # Hand-off counters of the fused quantise + GEMM kernel: one zeroed buffer per
-    # (device, stream); every launch leaves it zeroed, launches on one stream never overlap.
-    _sync_cache = {}
-
-    def _sync_buffer(self, x: torch.Tensor, M: int) -> torch.Tensor:
-        need = int(self._lib.hy3d_fused_sync_bytes(M)) // 4
-        key = (x.device.index, self._stream(x))
-        buf = self._sync_cache.get(key)
-        if buf is None or buf.numel() < need:
-            n = 4096
-            while n < need:
-                n *= 2
-            buf = torch.zeros(n, dtype=torch.int32, device=x.device)
-            self._sync_cache[key] = buf
-        return buf
-
-    def reset_fused_sync(self):
-        """Re-zeroes the hand-off counters (only needed after a device-side timeout)."""
-        for buf in self._sync_cache.values():
-            buf.zero_()
-
-    def int8_linear_tc_fused(self, x, w_int8, w_scale, bias, epilogue=EPI_LINEAR, block_n=0):
-        """``int8_linear_tc`` as one launch: the activation quantiser runs inside the GEMM
-        kernel (the role of the reference's fused path, csrc/int8_sparse_tc.cu:1934-2070).
-        Bit-identical to the two-launch path."""
+    def int8_linear_tc_fused(self, x, w_int8, w_scale, bias, epilogue=EPI_LINEAR, block_n=0,
+                             return_scales=False):
+        """``int8_linear_tc`` as one launch with the quantised activations resident in shared
+        memory (the role of the reference's fused path, csrc/int8_sparse_tc.cu:1934-2002).
+        Bit-identical to the two-launch path; raises for shapes the kernel does not take
+        (K > 1280, K % 32 != 0)."""
         self._req(x, "x", (torch.float16, torch.bfloat16), 2)
         self._req(w_int8, "w_int8", torch.int8, 2)
         M, K = x.shape
         N = w_int8.shape[0]
         if w_int8.shape[1] != K:
             raise RuntimeError(f"K mismatch: x has {K}, w_int8 has {w_int8.shape[1]}")
-        q = torch.empty((M, K), dtype=torch.int8, device=x.device)
-        s = torch.empty((M,), dtype=torch.float32, device=x.device)
         out = torch.empty(self._out_shape(M, N, epilogue), dtype=x.dtype, device=x.device)
-        sync = self._sync_buffer(x, M)
+        s = torch.empty((M,), dtype=torch.float32, device=x.device) if return_scales else None
         bptr, bcode = self._opt_bias(bias)
         with torch.cuda.device(x.device):
             self._check(self._lib.hy3d_linear_w8a8_dense_fused(
-                x.data_ptr(), _DTYPE_CODE[x.dtype], K, q.data_ptr(), s.data_ptr(), sync.data_ptr(),
+                x.data_ptr(), _DTYPE_CODE[x.dtype], K, s.data_ptr() if s is not None else None,
                 w_int8.data_ptr(), w_scale.data_ptr(), _DTYPE_CODE[w_scale.dtype], bptr, bcode,
                 out.data_ptr(), _DTYPE_CODE[x.dtype], M, N, K, epilogue, block_n,
                 self._stream(x)), "hy3d_linear_w8a8_dense_fused")
-        return out
+        return (out, s) if return_scales else out
+
+    def int8_linear_path(self, M, K, N, epilogue=EPI_LINEAR):
+        """1 when ``int8_linear_tc`` runs this shape as one launch, 0 for two (the dense
+        counterpart of csrc/int8_sparse_tc.cu:2065-2070)."""
+        return int(self._lib.hy3d_linear_path(M, K, N, epilogue))
 
     def int8_linear_tc(self, x, w_int8, w_scale, bias, epilogue=EPI_LINEAR, cta_group=0, block_n=0):
         """x (M,K) f16/bf16, w_int8 (N,K), w_scale (N), bias (N) or empty -> (M,N) in x's
         dtype.  csrc/int8_gemm_tc.cu:312-320."""
-        if cta_group == 0 and os.environ.get("HY3D_FUSED_QUANT", "0") == "1":
-            return self.int8_linear_tc_fused(x, w_int8, w_scale, bias, epilogue, block_n)
         self._req(x, "x", (torch.float16, torch.bfloat16), 2)
         self._req(w_int8, "w_int8", torch.int8, 2)
         M, K = x.shape
@@ -390,8 +398,9 @@ class SparseTcModule(_Base):
         return self.sparse_int8_linear_ex(x, w_comp, w_meta, w_scale, bias, -1)
 
     def sparse_int8_linear_path(self, M, K, N):
-        """csrc/int8_sparse_tc.cu:2065-2070 reported which of two code paths a shape takes;
-        this library has one path."""
+        """csrc/int8_sparse_tc.cu:2065-2070 reported which of two code paths a shape takes
+        (1 = quantiser fused into the GEMM).  The sparse layer here always runs its
+        quantiser and its GEMM as two launches."""
         return 0
 
     def test_mma_sp(self, a_comp, b, meta):

@@ -31,7 +31,7 @@ LIB_PATH = os.path.join(_CSRC, LIB_NAME)
 # hy3d_int8.cu is the only translation unit; it #includes the kernel files listed in HEADERS.
 SOURCES = ["hy3d_int8.cu"]
 HEADERS = ["common.cuh", "quantize.cu", "prune_pack.cu", "gemm_dense.cu", "gemm_sparse.cu",
-           "capi.cu", "static_scratch.cu", os.path.join(_REPO_INCLUDE, "hy3d_int8.h")]
+           "linear_fused.cu", "capi.cu", "static_scratch.cu", os.path.join(_REPO_INCLUDE, "hy3d_int8.h")]
 
 _lock = threading.Lock()
 _lib = None
@@ -98,7 +98,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 def _build_locked(stamp: str, digest: str, verbose: bool) -> str:
     nvcc = _nvcc()
-    flags = cuda_flags() + (["-Xptxas", "-v"] if verbose else [])
+    # The digest of the sources is baked into the library (hy3d_source_digest()), so a loaded
+    # .so can be told apart from one built from other sources.
+    flags = cuda_flags() + [f'-DHY3D_SOURCE_DIGEST="{digest}"'] + (["-Xptxas", "-v"] if verbose else [])
 
     def compile_one(src: str) -> str:
         obj = os.path.join(_BUILD_DIR, src.replace(".cu", ".o"))
@@ -133,14 +135,26 @@ def load_library(build_if_missing: bool = True) -> ctypes.CDLL:
         path = LIB_PATH
         if build_if_missing:
             try:
-                path = build()
-            except Exception:
-                # A box without nvcc can still use a library that travelled with the tree.
-                if not os.path.exists(LIB_PATH):
-                    raise
+                _nvcc()
+                have_nvcc = True
+            except RuntimeError:
+                have_nvcc = False
+            if have_nvcc:
+                path = build()          # compile and link errors propagate
+            elif not os.path.exists(LIB_PATH):
+                raise RuntimeError(f"{LIB_NAME} is missing and there is no nvcc to build it")
         if not os.path.exists(path):
             raise RuntimeError(f"{LIB_NAME} is missing; run `python csrc/build.py`")
-        _lib = ctypes.CDLL(path)
+        lib = ctypes.CDLL(path)
+        # A library that travelled with the tree must come from these sources: a stale one
+        # could be driven with argument lists it does not have.
+        lib.hy3d_source_digest.restype = ctypes.c_char_p
+        lib.hy3d_source_digest.argtypes = []
+        built_from = lib.hy3d_source_digest().decode()
+        if built_from != _source_digest():
+            raise RuntimeError(f"{LIB_NAME} was built from other sources (digest {built_from[:12]}...); "
+                               "rebuild it with `python csrc/build.py`")
+        _lib = lib
         return _lib
 
 

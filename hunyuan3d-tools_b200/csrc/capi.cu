@@ -72,6 +72,31 @@ int current_device() {
   return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
 }
 
+// Kernels here ask for more dynamic shared memory than the default limit; the attribute is
+// set once per (device, kernel).  Callers may launch from several host threads.
+int ensure_max_smem(const void* kernel, int bytes) {
+  constexpr int kSlots = 256;
+  static std::mutex mu;
+  static const void* seen_fn[kSlots];
+  static int seen_dev[kSlots];
+  static int n_seen = 0;
+  const int dev = current_device();
+  if (dev < 0) return HY3D_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < n_seen; ++i)
+    if (seen_fn[i] == kernel && seen_dev[i] == dev) return HY3D_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return HY3D_ERR_CUDA;
+  }
+  if (n_seen < kSlots) {
+    seen_fn[n_seen] = kernel;
+    seen_dev[n_seen] = dev;
+    ++n_seen;
+  }
+  return HY3D_OK;
+}
+
 // 2-D byte tensor: `rows` rows of `inner_bytes` bytes, `pitch_bytes` apart; the box is
 // box_inner bytes x box_rows rows.  Out-of-range parts of a box read as zero.
 int encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t inner_bytes, uint64_t rows,
@@ -113,7 +138,13 @@ int hy3d_trace_read(unsigned long long* out, int next_cta) {
 }
 #endif
 
-int hy3d_version(void) { return 100; }
+// Bumped whenever an entry point's argument list or meaning changes; the Python binding
+// refuses a library whose number differs from the one it was written against.
+int hy3d_version(void) { return HY3D_ABI_VERSION; }
+#ifndef HY3D_SOURCE_DIGEST
+#define HY3D_SOURCE_DIGEST "unknown"
+#endif
+const char* hy3d_source_digest(void) { return HY3D_SOURCE_DIGEST; }
 const char* hy3d_arch(void) { return "sm_100a"; }
 
 const char* hy3d_status_string(int status) {
@@ -140,6 +171,27 @@ int hy3d_last_device_status(int* status_out) {
   }
   *status_out = v;
   return HY3D_OK;
+}
+
+int hy3d_stream_status(void* stream) {
+  if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return HY3D_ERR_CUDA;
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return HY3D_ERR_CUDA;
+  return v == 0 ? HY3D_OK : HY3D_ERR_TIMEOUT;
+}
+
+int hy3d_set_wait_limit_ns(unsigned long long limit_ns) {
+  if (limit_ns == 0) limit_ns = kWaitLimitNs;
+  if (cudaMemcpyToSymbol(g_wait_limit_ns, &limit_ns, sizeof(limit_ns)) != cudaSuccess)
+    return HY3D_ERR_CUDA;
+  return HY3D_OK;
+}
+
+int hy3d_wait_selftest(void* stream) {
+  const int rc = check_device();
+  if (rc != HY3D_OK) return rc;
+  wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>();
+  return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
 }
 
 int hy3d_quantize_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* q,
@@ -174,43 +226,33 @@ int hy3d_linear_w8a8_dense(const void* x, int x_dtype, int64_t ldx, int8_t* q_ws
   int rc = check_device();
   if (rc != HY3D_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // One launch with the quantised activations resident in shared memory where that is the
+  // faster path (and the caller left tile shape and grouping to the library); same bits.
+  if (cta_group == 0 && block_n == 0 && x_dtype == out_dtype && (ldx & 7) == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      linear_path(M, K, N, epilogue) == 1)
+    return linear_fused(x, x_dtype, ldx, nullptr, B, w_scale, w_scale_dtype, bias, bias_dtype, out,
+                        out_dtype, M, N, K, epilogue, 0, s);
   rc = quantize_rows(x, x_dtype, M, K, ldx, q_ws, scale_ws, s);
   if (rc != HY3D_OK) return rc;
   return gemm_dense(q_ws, B, scale_ws, w_scale, w_scale_dtype, bias, bias_dtype, out, out_dtype, M,
                     N, K, epilogue, cta_group, block_n, s);
 }
 
-size_t hy3d_fused_sync_bytes(int64_t M) {
-  if (M < 0) return 0;
-  return static_cast<size_t>(2 + (M + 127) / 128) * sizeof(int32_t);
+int hy3d_linear_path(int64_t M, int64_t K, int64_t N, int epilogue) {
+  if (check_device() != HY3D_OK) return 0;
+  return linear_path(M, K, N, epilogue);
 }
 
-int hy3d_linear_w8a8_dense_fused(const void* x, int x_dtype, int64_t ldx, int8_t* q_ws,
-                                 float* scale_ws, int32_t* sync_ws, const int8_t* B,
-                                 const void* w_scale, int w_scale_dtype, const void* bias,
-                                 int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
-                                 int64_t K, int epilogue, int block_n, void* stream) {
-  int rc = check_device();
+int hy3d_linear_w8a8_dense_fused(const void* x, int x_dtype, int64_t ldx, float* scale_out,
+                                 const int8_t* B, const void* w_scale, int w_scale_dtype,
+                                 const void* bias, int bias_dtype, void* out, int out_dtype,
+                                 int64_t M, int64_t N, int64_t K, int epilogue, int block_n,
+                                 void* stream) {
+  const int rc = check_device();
   if (rc != HY3D_OK) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // The in-kernel quantiser reads the activations in the output's 16-bit type from
-  // 16-byte-aligned rows; anything else takes the two-launch path (same results).
-  const bool can_fuse = x && sync_ws && x_dtype == out_dtype &&
-                        (x_dtype == HY3D_F16 || x_dtype == HY3D_BF16) && (ldx & 7) == 0 &&
-                        (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-  if (!can_fuse) {
-    rc = quantize_rows(x, x_dtype, M, K, ldx, q_ws, scale_ws, s);
-    if (rc != HY3D_OK) return rc;
-    return gemm_dense(q_ws, B, scale_ws, w_scale, w_scale_dtype, bias, bias_dtype, out, out_dtype,
-                      M, N, K, epilogue, 1, block_n, s);
-  }
-  if (M > 0 && (!q_ws || !scale_ws)) return HY3D_ERR_ARG;
-  FusedInput f;
-  f.x = x;
-  f.ldx = ldx;
-  f.sync = sync_ws;
-  return gemm_dense(q_ws, B, scale_ws, w_scale, w_scale_dtype, bias, bias_dtype, out, out_dtype, M,
-                    N, K, epilogue, 1, block_n, s, &f);
+  return linear_fused(x, x_dtype, ldx, scale_out, B, w_scale, w_scale_dtype, bias, bias_dtype, out,
+                      out_dtype, M, N, K, epilogue, block_n, static_cast<cudaStream_t>(stream));
 }
 
 int hy3d_prune_pack_24(const int8_t* w, int64_t N, int64_t K, int8_t* comp, uint8_t* meta_raw,

@@ -11,6 +11,8 @@
 
 #include "../../include/hy3d_int8.h"
 
+#define HY3D_ABI_VERSION 200
+
 namespace hy3d {
 
 // ------------------------------------------------------------------------------------
@@ -167,6 +169,8 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 // (whole launches last well under 10 ms) and short enough that a protocol error ends the
 // kernel instead of hanging the device.
 constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
+// The limit in force; tests shorten it to a few milliseconds (hy3d_set_wait_limit_ns).
+__device__ unsigned long long g_wait_limit_ns = kWaitLimitNs;
 
 // Bounded wait.  `abort_flag` lives in shared memory and is set by whichever role times
 // out first, so the other roles leave their waits promptly.  Returns false on give-up.
@@ -185,13 +189,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      if (now - t0 > g_wait_limit_ns) {
         *abort_flag = 1;
         atomicCAS(&g_device_status, 0, err_code);
         return false;
       }
     }
   }
+}
+
+// Exercises the give-up path of the bounded wait without disturbing anything else: one thread
+// waits on an mbarrier that nobody will ever arrive on; once the limit in force runs out it
+// records kDevTimeoutFull in the device status word and the kernel returns normally.
+__global__ void wait_selftest_kernel() {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, kDevTimeoutFull);
+    mbar_inval(smem_u32(&bar));
+  }
+  __syncthreads();
 }
 
 // ------------------------------------------------------------------------------------

@@ -15,16 +15,6 @@
 // Two accumulator buffers in tensor memory let the epilogue of tile i overlap the MMAs of
 // tile i+1.  Every wait is bounded; a wait that runs out records a code in the device
 // status word and all roles fall through to the common teardown.
-//
-// Fused activation quantiser (kFused): the kernel is given the fp16 / bf16 activations instead
-// of int8 codes.  Whenever an epilogue warp finds no finished accumulator it claims eight rows
-// of the activation matrix from a global ticket counter, quantises them (same arithmetic as
-// quantize_rows_kernel) into the int8 workspace the A tensor map points at, and bumps the
-// ready counter of that 128-row tile; the TMA producer of whichever CTA needs the tile waits
-// for the counter to reach 16 before its first A load.  A claimed batch never waits on
-// anything, so the hand-off cannot deadlock however the CTAs are scheduled; the int8 codes
-// make their round trip through L2 while the quantiser work hides behind the MMAs.  The last
-// CTA to finish returns the counters to zero for the next launch.
 #include "common.cuh"
 #include <cstdlib>
 
@@ -34,6 +24,8 @@ int encode_tmap_2d_u8(CUtensorMap* map, const void* base, uint64_t inner_bytes, 
                       uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, int swizzle_bytes);
 int device_sm_count();
 int current_device();
+// Raises a kernel's dynamic shared-memory limit once per (device, kernel); thread-safe.
+int ensure_max_smem(const void* kernel, int bytes);
 
 namespace dense {
 namespace {
@@ -59,136 +51,8 @@ struct DenseArgs {
   int block_n, stages, acc_cols, tma_store, store_bufs;
   int m_tiles, n_tiles, num_kb, last_ksteps, n_fastest;
   int atoms;   // 128-byte K blocks per pipeline stage (1 or 2)
-  int debug;   // diagnostic switches (HY3D_DEBUG): 1 no TMA loads, 2 no epilogue work, 4 no MMA
-  // Fused activation quantiser (all unused when the kernel is not instantiated with kFused).
-  const uint16_t* qx;   // fp16 / bf16 activations (M, K), row pitch q_ldx elements
-  int64_t q_ldx;
-  int8_t* q_out;        // int8 codes (M, K): the matrix the A tensor map reads
-  float* q_scale;       // per-row scales (M): the same array act_scale points at
-  int* q_sync;          // [0] ticket counter, [1] finished-CTA counter, [2 + t] ready count of tile t
-  int q_lanes_log2;     // lanes that share a row = 1 << q_lanes_log2 (4..32)
-  int q_vecs;           // 16-byte vectors per lane and row
-  int q_units;          // tickets: 16 per 128-row tile
+  int debug;   // knock-out switches of -DHY3D_TRACE builds (always 0 in the shipped library)
 };
-
-constexpr int kQuantUnitRows = 8;                          // rows per ticket
-constexpr int kQuantUnitsPerTile = kTileM / kQuantUnitRows;
-
-// Quantises the rows row0 .. row0 + (32 >> lanes_log2) - 1, one row per group of lanes.
-// Rows longer than 8 vectors per lane are read twice (absmax pass, then rounding pass).
-template <bool kBf16>
-__device__ __forceinline__ void quantize_row_batch(const DenseArgs& p, int row0, int lane) {
-  const int G = 1 << p.q_lanes_log2;
-  const int sub = lane & (G - 1);
-  const int64_t row = static_cast<int64_t>(row0) + (lane >> p.q_lanes_log2);
-  const bool row_ok = row < p.M;
-  const int nvec = p.K >> 3;
-  const int V = p.q_vecs;
-  const int nchunk = (V + 7) >> 3;
-  const uint4* src = reinterpret_cast<const uint4*>(p.qx + (row_ok ? row : 0) * p.q_ldx);
-  uint4 v[8];
-  uint32_t amax2 = 0;
-  for (int ch = 0; ch < nchunk; ++ch) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int c = sub + ((ch << 3) + i) * G;
-      if ((ch << 3) + i < V) {
-        if (row_ok && c < nvec) v[i] = nchunk == 1 ? __ldcs(src + c) : __ldcg(src + c);
-        else v[i] = make_uint4(0, 0, 0, 0);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if ((ch << 3) + i < V) quant::absmax8<kBf16>(v[i], amax2);
-    }
-  }
-  float amax = quant::absmax_to_float<kBf16>(amax2);
-  for (int off = G >> 1; off > 0; off >>= 1)
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
-  const float inv = __frcp_rn(scale);
-  if (row_ok && sub == 0) p.q_scale[row] = scale;
-  uint2* dst = reinterpret_cast<uint2*>(p.q_out + (row_ok ? row : 0) * static_cast<int64_t>(p.K));
-  for (int ch = nchunk - 1; ch >= 0; --ch) {
-    if (ch != nchunk - 1) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int c = sub + ((ch << 3) + i) * G;
-        if (row_ok && c < nvec) v[i] = __ldcs(src + c);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int c = sub + ((ch << 3) + i) * G;
-      if ((ch << 3) + i < V && row_ok && c < nvec) {
-        float f[8];
-        quant::unpack8<kBf16>(v[i], f);
-        dst[c] = quant::quant8(f, scale, inv);
-      }
-    }
-  }
-}
-
-// Work-claiming state of one epilogue warp (warp-uniform).
-struct QuantWorker {
-  int unit = -1;       // claimed ticket, -1 = none
-  int row = 0;         // next row of the ticket to quantise
-  bool drained = false;
-};
-
-// One step of quantiser work: claims a ticket if the warp holds none, quantises one batch of
-// rows, and publishes the ticket once its eight rows are done.  Returns false when no work is
-// left for this warp.
-template <bool kBf16>
-__device__ __forceinline__ bool quantize_step(const DenseArgs& p, QuantWorker& w, int lane) {
-  if (w.drained) return false;
-  if (w.unit < 0) {
-    int t = 0;
-    if (lane == 0) t = atomicAdd(p.q_sync, 1);
-    t = __shfl_sync(0xffffffffu, t, 0);
-    if (t >= p.q_units) { w.drained = true; return false; }
-    w.unit = t;
-    w.row = 0;
-  }
-  quantize_row_batch<kBf16>(p, w.unit * kQuantUnitRows + w.row, lane);
-  w.row += 32 >> p.q_lanes_log2;
-  if (w.row >= kQuantUnitRows) {
-    // Every lane's stores are ordered before lane 0's release of the tile counter; the proxy
-    // fence covers the reader being a bulk tensor copy.
-    asm volatile("fence.proxy.async.global;" ::: "memory");
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence();
-      atomicAdd(p.q_sync + 2 + w.unit / kQuantUnitsPerTile, 1);
-    }
-    w.unit = -1;
-  }
-  return true;
-}
-
-// Producer side of the hand-off: bounded wait until all tickets of a 128-row tile are in.
-__device__ __forceinline__ bool wait_tile_quantized(const int* counter, volatile int* abort_flag) {
-  uint64_t t0 = 0;
-  uint32_t spins = 0;
-  while (true) {
-    int v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
-    if (v >= kQuantUnitsPerTile) break;
-    if ((++spins & 0x3Fu) == 0) {
-      if (*abort_flag) return false;
-      const uint64_t now = global_timer_ns();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        atomicCAS(&g_device_status, 0, static_cast<int>(kDevTimeoutQuant));
-        return false;
-      }
-    }
-    __nanosleep(40);
-  }
-  asm volatile("fence.proxy.async.global;" ::: "memory");
-  return true;
-}
 
 struct __align__(16) DenseCtrl {
   float ws[256];        // per-column weight scales of the current tile columns
@@ -286,7 +150,7 @@ __device__ __forceinline__ void slab_store(const uint32_t (&packed)[16], uint32_
   }
 }
 
-template <bool kBf16, int kEpi, int kG, bool kFused, int kAtoms>
+template <bool kBf16, int kEpi, int kG, int kAtoms>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_o, const DenseArgs p) {
@@ -363,23 +227,20 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      int ready_m = -1;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         const int m0 = tile_m(tile) * (kTileM * kG) + row_off;
         const int n0 = tile_n(tile) * p.block_n + col_off;
-        if (kFused && tile_m(tile) != ready_m) {
-          ok = wait_tile_quantized(p.q_sync + 2 + tile_m(tile), abort_flag);
-          if (!ok) break;
-          ready_m = tile_m(tile);
-        }
         for (int kb = 0; kb < p.num_kb; ++kb) {
           ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
           if (!ok) break;
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_base + stage * stage_bytes;
+#ifdef HY3D_TRACE
           if (p.debug & 1) {
             if (leader) mbar_arrive(full);
-          } else if (kG == 1) {
+          } else
+#endif
+          if (kG == 1) {
             mbar_arrive_expect_tx(full, stage_bytes);
 #pragma unroll
             for (int a = 0; a < kAtoms; ++a) {
@@ -421,7 +282,11 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t stage_step = stage_bytes >> 4;
       const uint32_t a_atom = a_bytes >> 4, b_atom = b_bytes >> 4;
       const uint32_t b_off = static_cast<uint32_t>(kAtoms) * a_atom;
+#ifdef HY3D_TRACE
       const bool do_mma = !(p.debug & 4);
+#else
+      constexpr bool do_mma = true;
+#endif
       // stages with the full 4 K steps per 128-byte block
       const int full_kb = p.last_ksteps == 4 * kAtoms ? p.num_kb : p.num_kb - 1;
       int stage = 0;
@@ -527,8 +392,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // per-column scales / bias are refilled only when the tile column changes (with the grid
     // a multiple of the column count, a CTA keeps its column for the whole launch).
     float as_next = 0.0f;
-    QuantWorker qw;
-    if (!kFused && scaled && first_tile < total_tiles) {
+    if (scaled && first_tile < total_tiles) {
       const int m_first = tile_m(first_tile) * (kTileM * kG) + row_off + row_in_tile;
       if (m_first < p.M) as_next = p.act_scale[m_first];
     }
@@ -538,7 +402,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const int m0 = tile_m(tile) * (kTileM * kG) + row_off;
       const int n0 = tile_n(tile) * p.block_n;
       float as = as_next;
-      if (!kFused) {
+      {
         const int nt = tile + tile_step;
         as_next = 0.0f;
         if (scaled && nt < total_tiles) {
@@ -557,13 +421,6 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         cur_n0 = n0;
       }
       const long long w0c = HY3D_CLK();
-      if (kFused) {
-        // No finished accumulator yet: spend the time on the activation quantiser.
-        while (ok && !mbar_test_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase)) {
-          if (*abort_flag) { ok = false; break; }
-          if (!quantize_step<kBf16>(p, qw, lane)) break;
-        }
-      }
       if (ok) ok = mbar_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag,
                              kDevTimeoutTmemFull);
       const long long w1c = HY3D_CLK();
@@ -574,15 +431,17 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       if (threadIdx.x == 64) HY3D_TRACE_EVENT(2, tr, 4, it);
       const int m = m0 + row_in_tile;
       const bool row_ok = m < p.M;
-      // The scales of a fused launch were written during this kernel (possibly by another
-      // SM): read them from L2 once the accumulators, and with them the tile, are known ready.
-      if (kFused) as = row_ok ? __ldcg(p.act_scale + m) : 0.0f;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(buf * p.acc_cols);
       const float* wsb = ctrl->ws;
       const float* bsb = ctrl->bs;
       bool arrived = false;
-      if (p.tma_store && !(p.debug & 2)) {
+#ifdef HY3D_TRACE
+      const bool skip_epilogue = (p.debug & 2) != 0;
+#else
+      constexpr bool skip_epilogue = false;
+#endif
+      if (p.tma_store && !skip_epilogue) {
         const int nslab = p.block_n / acc_per_slab;
         const int out_row = m0 + quarter * 32;
         const bool rows_in = out_row < p.M;
@@ -693,10 +552,6 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         release_acc(smem_u32(&ctrl->tmem_empty[buf]));
       }
     }
-    if (kFused) {
-      // Tiles done: help until every ticket has been claimed, and finish a ticket in hand.
-      while (!*abort_flag && quantize_step<kBf16>(p, qw, lane)) { }
-    }
     if (threadIdx.x == 64) {
       HY3D_TRACE_RAW(4, acc_tile); HY3D_TRACE_RAW(5, acc_wait); HY3D_TRACE_RAW(6, it);
     }
@@ -716,17 +571,6 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   // Neither CTA of a pair may retire while the other can still touch its shared memory,
   // barriers or tensor memory.
   if (kG == 2) cluster_sync_all();
-  if (kFused && threadIdx.x == 0) {
-    // The last CTA to get here (all tickets are done, nobody reads the counters any more)
-    // zeroes them for the next launch that uses this workspace.
-    __threadfence();
-    if (atomicAdd(p.q_sync + 1, 1) == static_cast<int>(gridDim.x) - 1) {
-      for (int t = 0; t < p.m_tiles; ++t) p.q_sync[2 + t] = 0;
-      p.q_sync[0] = 0;
-      __threadfence();
-      p.q_sync[1] = 0;
-    }
-  }
   if (warp == 1) {
     tc_fence_after_sync();
     if (kG == 2) tmem_dealloc_2cta(tmem_base, static_cast<uint32_t>(2 * p.acc_cols));
@@ -736,18 +580,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 
 }  // namespace
 
-// Activations for a launch with the quantiser fused in: `A` / `act_scale` of gemm_dense are
-// then the int8 / scale workspaces the kernel fills itself.
-struct FusedInput {
-  const void* x;    // fp16 or bf16 (the output dtype), (M, K)
-  int64_t ldx;      // row pitch in elements, a multiple of 8
-  int* sync;        // (2 + ceil(M / 128)) int32, zero on entry, zero again on exit
-};
-
 int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale,
                int ws_dtype, const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M,
                int64_t N, int64_t K, int epilogue, int cta_group, int block_n,
-               cudaStream_t stream, const FusedInput* fused = nullptr) {
+               cudaStream_t stream) {
   if (out_dtype != HY3D_F16 && out_dtype != HY3D_BF16 && out_dtype != HY3D_S32) return HY3D_ERR_ARG;
   if (epilogue < HY3D_EPI_LINEAR || epilogue > HY3D_EPI_GEGLU) return HY3D_ERR_ARG;
   if (out_dtype == HY3D_S32 && epilogue != HY3D_EPI_LINEAR) return HY3D_ERR_ARG;
@@ -802,14 +638,10 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
     const int sms = device_sm_count() > 0 ? device_sm_count() : 148;
     const int64_t pair_tiles = ((M + 2 * kTileM - 1) / (2 * kTileM)) * ((N + block_n - 1) / block_n);
     const int64_t min_pair_tiles = K >= 2048 ? (sms / 2) * 4 / 5 : 4 * (sms / 2);
-    group = (!fused && K >= 1024 && (block_n & 31) == 0 && pair_tiles >= min_pair_tiles) ? 2 : 1;
+    group = (K >= 1024 && (block_n & 31) == 0 && pair_tiles >= min_pair_tiles) ? 2 : 1;
+#ifdef HY3D_TRACE
     if (const char* e = getenv("HY3D_CTA_GROUP")) group = atoi(e) == 2 ? 2 : 1;
-  }
-  if (fused) {
-    if (out_dtype == HY3D_S32 || !fused->x || !fused->sync || (K & 7) || (fused->ldx & 7) ||
-        fused->ldx < K || (reinterpret_cast<uintptr_t>(fused->x) & 15))
-      return HY3D_ERR_SHAPE;
-    group = 1;
+#endif
   }
   if (group == 2 && (block_n & 31)) {
     if (cta_group == 2) return HY3D_ERR_SHAPE;
@@ -844,34 +676,24 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
     const int fixed1 = fixed2 - kEpiWarps * kSlabBytes;
     const int stages2 = (kSmemLimit - fixed2) / stage_bytes, stages1 = (kSmemLimit - fixed1) / stage_bytes;
     if (stages2 < 4 && stages1 > stages2) store_bufs = 1;
+#ifdef HY3D_TRACE
     if (const char* e = getenv("HY3D_STORE_BUFS")) store_bufs = atoi(e) == 1 ? 1 : 2;
+#endif
   }
   p.store_bufs = store_bufs;
   const int fixed = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * store_bufs * kSlabBytes;
   int stages = (kSmemLimit - fixed) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
+#ifdef HY3D_TRACE
   if (const char* e = getenv("HY3D_STAGES")) { const int v = atoi(e); if (v >= 2 && v < stages) stages = v; }
+#endif
   if (stages < 2) return HY3D_ERR_SHAPE;
   p.stages = stages;
+  p.debug = 0;
+#ifdef HY3D_TRACE
   { const char* e = getenv("HY3D_DEBUG"); p.debug = e ? atoi(e) : 0; }
+#endif
   const int smem_bytes = stages * stage_bytes + fixed;
-  p.qx = nullptr; p.q_ldx = 0; p.q_out = nullptr; p.q_scale = nullptr; p.q_sync = nullptr;
-  p.q_lanes_log2 = 5; p.q_vecs = 0; p.q_units = 0;
-  if (fused) {
-    p.qx = static_cast<const uint16_t*>(fused->x);
-    p.q_ldx = fused->ldx;
-    p.q_out = const_cast<int8_t*>(A);
-    p.q_scale = const_cast<float*>(act_scale);
-    p.q_sync = fused->sync;
-    // Lanes per row: the power of two (4..32) nearest to five 16-byte vectors per lane, so
-    // short rows keep all 32 lanes busy by taking several rows per warp.
-    const int nvec = static_cast<int>(K >> 3);
-    int lg = 2;
-    while (lg < 5 && (nvec + (1 << lg) - 1) / (1 << lg) > 5) ++lg;
-    p.q_lanes_log2 = lg;
-    p.q_vecs = (nvec + (1 << lg) - 1) >> lg;
-    p.q_units = p.m_tiles * kQuantUnitsPerTile;
-  }
 
   CUtensorMap tm_a, tm_b, tm_o;
   int rc = encode_tmap_2d_u8(&tm_a, A, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
@@ -891,29 +713,20 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   }
 
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const DenseArgs);
-  // [0]: one CTA per tile, [1]: CTA pairs, [2]: one CTA per tile with the quantiser fused in,
-  // [3]: CTA pairs with deep (two-block) stages.
-#define HY3D_DENSE_ROW(G, F, A)                                                              \
-  {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, G, F, A>, gemm_dense_kernel<false, HY3D_EPI_GELU, G, F, A>, \
-    gemm_dense_kernel<false, HY3D_EPI_GEGLU, G, F, A>},                                        \
-   {gemm_dense_kernel<true, HY3D_EPI_LINEAR, G, F, A>, gemm_dense_kernel<true, HY3D_EPI_GELU, G, F, A>,   \
-    gemm_dense_kernel<true, HY3D_EPI_GEGLU, G, F, A>}}
-  static const KernelFn kernels[4][2][3] = {HY3D_DENSE_ROW(1, false, 1), HY3D_DENSE_ROW(2, false, 1),
-                                            HY3D_DENSE_ROW(1, true, 1), HY3D_DENSE_ROW(2, false, 2)};
+  // [0]: one CTA per tile, [1]: CTA pairs, [2]: CTA pairs with deep (two-block) stages.
+#define HY3D_DENSE_ROW(G, A)                                                              \
+  {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, G, A>, gemm_dense_kernel<false, HY3D_EPI_GELU, G, A>, \
+    gemm_dense_kernel<false, HY3D_EPI_GEGLU, G, A>},                                        \
+   {gemm_dense_kernel<true, HY3D_EPI_LINEAR, G, A>, gemm_dense_kernel<true, HY3D_EPI_GELU, G, A>,   \
+    gemm_dense_kernel<true, HY3D_EPI_GEGLU, G, A>}}
+  static const KernelFn kernels[3][2][3] = {HY3D_DENSE_ROW(1, 1), HY3D_DENSE_ROW(2, 1), HY3D_DENSE_ROW(2, 2)};
 #undef HY3D_DENSE_ROW
   // Raw int32 output runs the direct-store path of the <false, LINEAR> instance.
   const int ki = out_dtype == HY3D_BF16 ? 1 : 0;
-  const int variant = fused ? 2 : (group == 2 && atoms == 2 ? 3 : group - 1);
+  const int variant = (group == 2 && atoms == 2) ? 2 : group - 1;
   const KernelFn kernel = kernels[variant][ki][epilogue];
-  static bool attr_set[64][4][2][3] = {};
-  const int dev = current_device();
-  if (dev < 0 || dev >= 64) return HY3D_ERR_CUDA;
-  if (!attr_set[dev][variant][ki][epilogue]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
-        cudaSuccess)
-      return HY3D_ERR_CUDA;
-    attr_set[dev][variant][ki][epilogue] = true;
-  }
+  rc = ensure_max_smem(reinterpret_cast<const void*>(kernel), kSmemLimit);
+  if (rc != HY3D_OK) return rc;
   const int sms = device_sm_count();
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.m_tiles * p.n_tiles;
@@ -924,17 +737,18 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   // grid rounded down to a multiple of the column count every CTA keeps ONE tile column for
   // the whole launch, so its per-column scales and bias are staged once and the epilogue warps
   // never meet at a CTA-wide barrier again (measured faster or equal on every sweep shape).
-  // With the quantiser fused in, this is also the order in which the rows get quantised.
   p.n_fastest = 0;
   if (p.n_tiles > 1) {
     p.n_fastest = 1;
     if (p.n_tiles <= clusters / 4) clusters -= clusters % p.n_tiles;
   }
+#ifdef HY3D_TRACE
   if (const char* e = getenv("HY3D_ORDER")) {
     p.n_fastest = atoi(e) ? 1 : 0;
     clusters = total_tiles < max_clusters ? total_tiles : max_clusters;
     if (p.n_fastest && p.n_tiles <= clusters / 4) clusters -= clusters % p.n_tiles;
   }
+#endif
   const int grid = group * clusters;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -959,6 +773,5 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
 }  // namespace dense
 
 using dense::gemm_dense;
-using dense::FusedInput;
 
 }  // namespace hy3d

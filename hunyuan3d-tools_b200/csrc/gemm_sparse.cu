@@ -457,7 +457,9 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   {
     const int64_t padded = ((N + 2 * kTileW - 1) / (2 * kTileW)) * (2 * kTileW);
     if (K >= 1024 && M >= 2048 && (block_t & 31) == 0 && padded * 4 <= N * 5) group = 2;
+#ifdef HY3D_TRACE
     if (const char* e = getenv("HY3D_SPARSE_CTA_GROUP")) group = atoi(e) == 2 ? 2 : 1;
+#endif
     if (group == 2 && (block_t & 31)) group = 1;
   }
 
@@ -506,15 +508,8 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const CUtensorMap, const SparseArgs);
   const KernelFn kernel = group == 2 ? gemm_sparse_kernel<2> : gemm_sparse_kernel<1>;
-  static bool attr_set[64][2] = {};
-  const int dev = current_device();
-  if (dev < 0 || dev >= 64) return HY3D_ERR_CUDA;
-  if (!attr_set[dev][group - 1]) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
-        cudaSuccess)
-      return HY3D_ERR_CUDA;
-    attr_set[dev][group - 1] = true;
-  }
+  rc = ensure_max_smem(reinterpret_cast<const void*>(kernel), kSmemLimit);
+  if (rc != HY3D_OK) return rc;
   const int sms = device_sm_count();
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.w_tiles * p.t_tiles;
@@ -537,7 +532,7 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
     cudaGetLastError();
     return HY3D_ERR_CUDA;
   }
-  return HY3D_OK;
+  return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
 }
 
 }  // namespace sparse

@@ -4,5 +4,6 @@
 #include "prune_pack.cu"
 #include "gemm_dense.cu"
 #include "gemm_sparse.cu"
+#include "linear_fused.cu"
 #include "capi.cu"
 #include "static_scratch.cu"

@@ -200,7 +200,18 @@ class Int8Linear(nn.Module):
                 cur = getattr(self, name, None)
                 if cur is None or cur.shape != src.shape or cur.dtype != src.dtype:
                     device = self.weight_scale.device
+                    if name == "bias" and name not in self._buffers:
+                        # built with bias=False: the plain None attribute must make room
+                        del self.bias
                     self.register_buffer(name, torch.empty(src.shape, dtype=src.dtype, device=device))
+        # A checkpoint in the reference's layout (buffers only, quantize_utils.py:181-198) has
+        # no extra state: infer it from which buffers are filled.
+        if prefix + "_extra_state" not in state_dict:
+            comp = state_dict.get(prefix + "weight_sparse_comp")
+            dense = state_dict.get(prefix + "weight_int8_nk")
+            sparse = comp is not None and comp.numel() > 0 and (dense is None or dense.numel() == 0)
+            state_dict[prefix + "_extra_state"] = {"mode": "sparse" if sparse else "tc",
+                                                   "epilogue": "linear", "layout": "hy3d-int8-v1"}
         super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys,
                                       unexpected_keys, error_msgs)
 
@@ -332,14 +343,18 @@ def quantize_model_tensorcore(model, min_features=128, verbose=True):
     stats = {"total_params": 0, "quantized_params": 0, "skipped_params": 0, "num_replaced": 0}
     _replace_linear_tensorcore(model, min_features, stats)
     if verbose:
-        saved_mb = stats["quantized_params"] * 1 / 1e6
-        print(f"  Quantized {stats['num_replaced']} Linear layers -> Int8Linear [tcgen05 INT8 GEMM]")
-        print(f"  TC-eligible: {stats.get('tc_eligible', 0)} layers")
-        print(f"  Linear params: {stats['total_params'] / 1e6:.1f}M total, "
-              f"{stats['quantized_params'] / 1e6:.1f}M quantized, "
-              f"{stats['skipped_params'] / 1e6:.1f}M skipped (below {min_features} features)")
-        print(f"  Estimated VRAM saved: ~{saved_mb:.0f} MB")
+        print(_summary(stats, "dense tcgen05 INT8 GEMM", bytes_per_weight=1.0))
     return stats
+
+
+def _summary(stats, kind, bytes_per_weight):
+    """One-paragraph report of a replacement pass (what ``verbose=True`` prints)."""
+    q, t = stats["quantized_params"], stats["total_params"]
+    kept = stats.get("kept_fp16", 0)
+    return (f"  {stats['num_replaced']} nn.Linear -> Int8Linear ({kind}); "
+            f"{q / 1e6:.1f}M of {t / 1e6:.1f}M linear weights converted, "
+            f"{stats['skipped_params'] / 1e6:.1f}M in layers too small, {kept} layer(s) left as they were; "
+            f"weight memory {q * 2 / 1e6:.0f} MB (16-bit) -> {q * bytes_per_weight / 1e6:.0f} MB")
 
 
 def _replace_linear_tensorcore(module, min_features, stats):
@@ -368,16 +383,7 @@ def quantize_model_sparse(model, min_features=128, sparse_min_k=640, verbose=Tru
              "num_replaced": 0, "sparse_eligible": 0, "kept_fp16": 0}
     _replace_linear_sparse(model, min_features, sparse_min_k, stats)
     if verbose:
-        fp16_mb = stats["quantized_params"] * 2 / 1e6
-        sparse_mb = stats["quantized_params"] * 0.625 / 1e6
-        print(f"  Quantized {stats['num_replaced']} Linear layers -> sparse Int8Linear [2:4 tcgen05.mma.sp]")
-        print(f"  Sparse-eligible: {stats['sparse_eligible']} layers")
-        print(f"  Kept as FP16: {stats['kept_fp16']} layers "
-              f"(K < {sparse_min_k}, K % 64 != 0, or N % 16 != 0)")
-        print(f"  Linear params: {stats['total_params'] / 1e6:.1f}M total, "
-              f"{stats['quantized_params'] / 1e6:.1f}M quantized, "
-              f"{stats['skipped_params'] / 1e6:.1f}M skipped (below {min_features} features)")
-        print(f"  Estimated VRAM saved: ~{fp16_mb - sparse_mb:.0f} MB (vs FP16)")
+        print(_summary(stats, f"2:4 sparse tcgen05.mma.sp, K >= {sparse_min_k}", bytes_per_weight=0.625))
     return stats
 
 

@@ -40,14 +40,28 @@ extern "C" {
 #define HY3D_EPI_GEGLU   2  /* weights row-interleaved in blocks of 16 (value,gate):
                                y[m, j] = value * gelu_erf(gate); output has N/2 columns   */
 
-/* Library version and build architecture ("sm_100a"). */
+/* ABI version (changes whenever an argument list or its meaning does), build architecture
+ * ("sm_100a") and the digest of the sources the library was built from. */
 int         hy3d_version(void);
 const char* hy3d_arch(void);
+const char* hy3d_source_digest(void);
 const char* hy3d_status_string(int status);
 
 /* Reads (with a device synchronisation) and clears the device-side error word that a
  * kernel sets when one of its bounded waits ran out.  0 = no error recorded. */
 int hy3d_last_device_status(int* status_out);
+
+/* Waits for `stream` and returns HY3D_ERR_TIMEOUT if a kernel has recorded a bounded wait
+ * that ran out since the error word was last cleared (the output of that launch is then
+ * undefined), HY3D_OK otherwise.  Does not clear the word; hy3d_last_device_status does. */
+int hy3d_stream_status(void* stream);
+
+/* Test hooks of the bounded waits (no reference counterpart).  hy3d_set_wait_limit_ns sets the
+ * longest any device-side wait may last on the current device (0 restores the default of 2 s);
+ * hy3d_wait_selftest launches one thread that waits on a barrier nobody signals, so that the
+ * limit runs out, the error word is set and the kernel returns normally. */
+int hy3d_set_wait_limit_ns(unsigned long long limit_ns);
+int hy3d_wait_selftest(void* stream);
 
 /*
  * Per-token (per-row) symmetric absmax quantisation: for each of the M rows
@@ -107,26 +121,28 @@ int hy3d_linear_w8a8_dense(const void* x, int x_dtype, int64_t ldx,
                            int epilogue, int cta_group, int block_n, void* stream);
 
 /*
- * The same layer as ONE kernel: the activation quantiser runs inside the GEMM kernel (idle
- * epilogue warps quantise rows of x into q_ws / scale_ws eight at a time, the TMA producers
- * pick each 128-row tile up from L2 as soon as it is complete), so the int8 activations never
- * make the round trip through HBM between two launches.  Results are bit-identical to
- * hy3d_linear_w8a8_dense.  sync_ws: hy3d_fused_sync_bytes(M) bytes of int32 counters that
- * must be ZERO before the first use; every launch leaves them zero again, so one buffer per
- * stream can be reused by all layers (launches that may overlap need separate buffers; after a
- * device-side timeout re-zero it).  x_dtype must equal out_dtype and ldx % 8 == 0 for the
- * fused kernel; other combinations run the two-launch path.  cta_group is always 1.
- * Replaces: the fused quantise + GEMM path csrc/int8_sparse_tc.cu:657-734, 1934-2070
- * (sparse_gemm_fq_kernel, sparse_fq_launch) in its role, for the dense layer.
+ * The same layer as ONE kernel with the quantised activations resident in shared memory: a
+ * CTA quantises a block of 128 tokens straight into the swizzled operand tiles of the whole K
+ * and runs every weight tile assigned to it against that block, so the int8 activations never
+ * exist in global memory and the layer moves 2*M*K + N*K + 2*M*N bytes.  Results are
+ * bit-identical to hy3d_linear_w8a8_dense.  Needs x_dtype == out_dtype (f16 / bf16),
+ * K % 32 == 0, K <= 1280, ldx % 8 == 0, N % 16 == 0 (N % 32 for GEGLU) and 16-byte aligned
+ * pointers; anything else returns HY3D_ERR_SHAPE / HY3D_ERR_ARG and launches nothing.
+ * scale_out: optional (M) f32 array that receives the per-token scales, or NULL.
+ * block_n: 0 = choose, else the weight-tile width (multiple of 32, 64 for GEGLU, <= 256).
+ * hy3d_linear_w8a8_dense takes this path by itself for the shapes where it is the faster one;
+ * hy3d_linear_path(M, K, N, epilogue) tells which (1 = one launch, 0 = two launches).
+ * Replaces: the fused quantise + GEMM path csrc/int8_sparse_tc.cu:657-734, 1934-2002
+ * (sparse_gemm_fq_kernel, sp_use_fused, sparse_fq_launch) and the path query
+ * csrc/int8_sparse_tc.cu:2065-2070 (sparse_int8_linear_path), for the dense layer.
  */
-size_t hy3d_fused_sync_bytes(int64_t M);
-int hy3d_linear_w8a8_dense_fused(const void* x, int x_dtype, int64_t ldx,
-                                 int8_t* q_ws, float* scale_ws, int32_t* sync_ws,
+int hy3d_linear_w8a8_dense_fused(const void* x, int x_dtype, int64_t ldx, float* scale_out,
                                  const int8_t* B, const void* w_scale, int w_scale_dtype,
                                  const void* bias, int bias_dtype,
                                  void* out, int out_dtype,
                                  int64_t M, int64_t N, int64_t K,
                                  int epilogue, int block_n, void* stream);
+int hy3d_linear_path(int64_t M, int64_t K, int64_t N, int epilogue);
 
 /*
  * The dense linear layer again, for callers that may not allocate device memory where the
@@ -163,7 +179,8 @@ int64_t hy3d_static_scratch_max_rows(void);
  * one nibble idx0 | idx1<<2 per group.  meta_packed (optional): (N, meta_ld) uint32 words,
  * word c of a row = the 8 nibbles of K chunk [32c, 32c+32), least-significant first;
  * meta_ld >= K/32, words [K/32, meta_ld) of each row are written as 0x44444444.
- * Requires K % 32 == 0 (K % 16 when meta_packed is NULL), 16-byte aligned w rows.
+ * Requires K % 4 == 0; with meta_packed also K % 32 == 0 and 16-byte aligned w and comp
+ * (8-byte aligned meta_raw).  Matrices that meet the second rule take the vectorised kernel.
  * Replaces: csrc/int8_sparse_tc.cu:152-212 (prune_compress_kernel), 416-437
  * (pack_metadata_kernel), 1558-1585 (sparse_prune_compress), 1616-1665
  * (sparse_prune_and_pack).

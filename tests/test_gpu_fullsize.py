@@ -8,8 +8,7 @@ from oracle import oracle as O
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
-FULL = [(49152, 320, 320), (49152, 320, 2560), (49152, 1280, 320), (12288, 640, 5120),
-        (12288, 2560, 640), (3072, 1280, 10240), (3072, 5120, 1280), (924, 1024, 1280)]
+FULL = list(O.SWEEP_SHAPES)        # all twelve shapes of the sweep
 
 
 def _case(M, K, N, seed):
@@ -34,10 +33,30 @@ def test_dense_fullsize_sampled_rows_and_checksum(tc, ik, i, shape):
     col_sum = acc.to(torch.int64).sum(dim=0).cpu()
     expect = q.to(torch.int64).sum(dim=0).cpu() @ wq.to(torch.int64).t()
     assert torch.equal(col_sum, expect)
-    # (3) fused layer output on the sampled rows, inside the 1e-2 gate
+    # (3) whole layer (whichever path the library picks) on the sampled rows, inside the 1e-2 gate
     y = tc.int8_linear_tc(xg, wg, ws.to(DEV), b.to(DEV))
     ref = O.epilogue(O.int32_matmul(qo, wq), so, ws, b, torch.bfloat16)
     assert O.rel_l2(y[rows.to(DEV)], ref) < 1e-2
+    # (4) the one-launch path, where the kernel takes the shape, gives the same bits
+    if K <= 1280:
+        assert torch.equal(tc.int8_linear_tc_fused(xg, wg, ws.to(DEV), b.to(DEV)),
+                           tc.int8_linear_tc(xg, wg, ws.to(DEV), b.to(DEV), cta_group=1))
+
+
+@pytest.mark.parametrize("i,shape", [(i, s) for i, s in enumerate(FULL) if s[0] == 49152])
+def test_dense_fullsize_every_row_of_the_49152_token_shapes(tc, ik, i, shape):
+    """All rows, not a sample: codes, scales and int32 accumulators of the three 49152-token
+    layers against the CPU oracle (host int32 matmul of the same int8 tensors)."""
+    M, K, N = shape
+    x, wq, ws, b = _case(M, K, N, 100 + i)
+    q, s = ik.fused_quantize_activation(x.to(DEV))
+    qo, so = O.quantize_activation(x)
+    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    acc = tc.int8_gemm_tc(q, wq.to(DEV), None, None, None, out_dtype=torch.int32)
+    assert torch.equal(acc.cpu(), O.int32_matmul(qo, wq))
+    y = tc.int8_linear_tc(x.to(DEV), wq.to(DEV), ws.to(DEV), b.to(DEV))
+    ref = O.epilogue(O.int32_matmul(qo, wq), so, ws, b, torch.bfloat16)
+    assert O.rel_l2(y, ref) < 1e-4
 
 
 @pytest.mark.parametrize("i,shape", list(enumerate(FULL)))

@@ -1,6 +1,6 @@
-"""GPU: the dense linear layer with the activation quantiser fused into the GEMM kernel
-(one launch) against the two-launch path and the CPU oracle.  Integer hand-off, so every
-output bit must agree."""
+"""GPU: the dense linear layer as one launch (activations quantised into a resident
+shared-memory block) against the two-launch path and the CPU oracle.  Same integer codes and
+the same epilogue arithmetic, so every output bit must agree."""
 import pytest
 import torch
 
@@ -22,13 +22,12 @@ def _case(M, K, N, dtype, seed):
     (1000, 640, 320),       # ragged last tile, 16 lanes per row
     (333, 1280, 640),       # 32 lanes per row
     (924, 1024, 320),       # cross-attention K/V shape
-    (200, 2560, 640),       # rows read twice (more than 8 vectors per lane)
-    (130, 5120, 1280),
-    (1, 320, 320), (129, 64, 128), (77, 128, 16), (6000, 320, 2560)])
+    (2000, 1280, 1280),     # one resident block (K > 640), several tiles per block
+    (1, 320, 320), (129, 64, 128), (77, 128, 16), (6000, 320, 2560), (257, 96, 48)])
 def test_fused_equals_two_launch_path(tc, dtype, M, K, N):
     x, wq, ws, b = _case(M, K, N, dtype, seed=M + K + N)
     xd, wd, sd, bd = x.to(DEV), wq.to(DEV), ws.to(DEV), b.to(DEV)
-    y2 = tc.int8_linear_tc(xd, wd, sd, bd)
+    y2 = tc.int8_linear_tc(xd, wd, sd, bd, cta_group=1)     # cta_group given: always two launches
     y1 = tc.int8_linear_tc_fused(xd, wd, sd, bd)
     assert tc.device_status() == 0
     assert torch.equal(y1, y2)
@@ -41,43 +40,27 @@ def test_fused_epilogues(tc, mode, code):
     x, wq, ws, b = _case(777, 640, 1280, torch.bfloat16, seed=5)
     xd, wd, sd, bd = x.to(DEV), wq.to(DEV), ws.to(DEV), b.to(DEV)
     y1 = tc.int8_linear_tc_fused(xd, wd, sd, bd, epilogue=code)
-    y2 = tc.int8_linear_tc(xd, wd, sd, bd, epilogue=code)
+    y2 = tc.int8_linear_tc(xd, wd, sd, bd, epilogue=code, cta_group=1)
     assert tc.device_status() == 0
     assert torch.equal(y1, y2)
     assert O.rel_l2(y1, O.linear_w8a8(x, wq, ws, b, mode=mode)) < 2e-3
 
 
-def test_fused_workspaces_hold_the_quantiser_output_and_counters_return_to_zero(tc, ik):
-    """The int8 codes and scales the fused kernel leaves in its workspaces are the stand-alone
-    quantiser's, and the hand-off counters are zero again after every launch (so one buffer
-    serves every layer on the stream)."""
-    import ctypes
+def test_fused_scales_are_the_quantisers(tc, ik):
+    """The per-token scales the one-launch kernel reports are the stand-alone quantiser's
+    (and the oracle's), ragged last block included."""
     x, wq, ws, b = _case(3000, 1280, 640, torch.bfloat16, seed=9)
     xd, wd, sd, bd = x.to(DEV), wq.to(DEV), ws.to(DEV), b.to(DEV)
-    M, K = x.shape
-    N = wq.shape[0]
-    q = torch.empty(M, K, dtype=torch.int8, device=DEV)
-    s = torch.empty(M, dtype=torch.float32, device=DEV)
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    nbytes = int(tc._lib.hy3d_fused_sync_bytes(M))
-    assert nbytes == 4 * (2 + (M + 127) // 128)
-    sync = torch.zeros(nbytes // 4, dtype=torch.int32, device=DEV)
-    for _ in range(3):
-        rc = tc._lib.hy3d_linear_w8a8_dense_fused(
-            xd.data_ptr(), 1, K, q.data_ptr(), s.data_ptr(), sync.data_ptr(), wd.data_ptr(),
-            sd.data_ptr(), 1, bd.data_ptr(), 1, out.data_ptr(), 1, M, N, K, 0, 0,
-            torch.cuda.current_stream().cuda_stream)
-        assert rc == 0
-        torch.cuda.synchronize()
-        assert int(sync.abs().sum()) == 0
-    q_ref, s_ref = ik.fused_quantize_activation(xd)
-    assert torch.equal(q, q_ref) and torch.equal(s, s_ref)
-    qo, so = O.quantize_activation(x)
-    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    y, s = tc.int8_linear_tc_fused(xd, wd, sd, bd, return_scales=True)
+    _, s_ref = ik.fused_quantize_activation(xd)
+    assert torch.equal(s, s_ref)
+    _, so = O.quantize_activation(x)
+    assert torch.equal(s.cpu(), so)
+    assert torch.equal(y, tc.int8_linear_tc(xd, wd, sd, bd, cta_group=1))
     assert tc.device_status() == 0
 
 
-def test_fused_back_to_back_layers_share_one_counter_buffer(tc):
+def test_fused_back_to_back_layers(tc):
     """A chain of layers of different shapes on one stream, launched without host
     synchronisation in between."""
     torch.manual_seed(0)
@@ -96,27 +79,58 @@ def test_fused_back_to_back_layers_share_one_counter_buffer(tc):
             h = fn(h, wq, ws, empty)
         return h
     a = run(tc.int8_linear_tc_fused)
-    b = run(tc.int8_linear_tc)
+    b = run(lambda *args: tc.int8_linear_tc(*args, cta_group=1))
     assert tc.device_status() == 0
     assert torch.equal(a, b)
 
 
-def test_fused_unsupported_combinations_take_the_two_launch_path(tc):
-    """Mixed activation / output types are served by the two-launch path of the same entry
-    point; the fused kernel itself needs 16-byte aligned rows."""
-    x, wq, ws, b = _case(300, 320, 320, torch.float16, seed=1)
+@pytest.mark.parametrize("block_n", [32, 64, 128, 160, 192, 256])
+def test_fused_tile_widths(tc, block_n):
+    x, wq, ws, b = _case(1500, 640, 832, torch.bfloat16, seed=block_n)
     xd, wd, sd, bd = x.to(DEV), wq.to(DEV), ws.to(DEV), b.to(DEV)
-    M, K = x.shape
-    N = wq.shape[0]
-    q = torch.empty(M, K, dtype=torch.int8, device=DEV)
-    s = torch.empty(M, dtype=torch.float32, device=DEV)
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    sync = torch.zeros(16, dtype=torch.int32, device=DEV)
-    rc = tc._lib.hy3d_linear_w8a8_dense_fused(
-        xd.data_ptr(), 0, K, q.data_ptr(), s.data_ptr(), sync.data_ptr(), wd.data_ptr(),
-        sd.data_ptr(), 0, bd.data_ptr(), 0, out.data_ptr(), 1, M, N, K, 0, 0,
-        torch.cuda.current_stream().cuda_stream)
-    assert rc == 0
-    ref = O.linear_w8a8(x, wq, ws, b).float()
-    assert O.rel_l2(out.float(), ref) < 5e-3            # bf16 rounding of an fp16-computed reference
+    y1 = tc.int8_linear_tc_fused(xd, wd, sd, bd, block_n=block_n)
+    y2 = tc.int8_linear_tc(xd, wd, sd, bd, cta_group=1)
+    assert tc.device_status() == 0
+    assert torch.equal(y1, y2)
+
+
+def test_fused_many_blocks_per_cta(tc):
+    """More token blocks than SMs: every CTA walks several resident blocks (both operand
+    buffers and all four scale slots get reused), with a ragged last block."""
+    for (M, K, N) in [(148 * 128 * 5 + 77, 320, 320), (148 * 128 * 3 + 1, 1280, 320),
+                      (40000, 64, 640), (30000, 1024, 160)]:
+        x, wq, ws, b = _case(M, K, N, torch.bfloat16, seed=K)
+        xd, wd, sd, bd = x.to(DEV), wq.to(DEV), ws.to(DEV), b.to(DEV)
+        y1 = tc.int8_linear_tc_fused(xd, wd, sd, bd)
+        y2 = tc.int8_linear_tc(xd, wd, sd, bd, cta_group=1)
+        assert tc.device_status() == 0
+        assert torch.equal(y1, y2)
+        rows = torch.randint(0, M, (300,))
+        ref = O.linear_w8a8(x[rows], wq, ws, b)
+        assert O.rel_l2(y1[rows.to(DEV)], ref) < 1e-4
+
+
+def test_default_entry_point_picks_the_path_it_reports(tc):
+    """hy3d_linear_w8a8_dense answers with the same bits whichever path it takes, and
+    hy3d_linear_path says which one that is."""
+    for (M, K, N) in [(148 * 128 + 5, 320, 320), (1000, 320, 320), (20000, 2560, 640)]:
+        x, wq, ws, b = _case(M, K, N, torch.bfloat16, seed=3)
+        xd, wd, sd, bd = x.to(DEV), wq.to(DEV), ws.to(DEV), b.to(DEV)
+        path = tc.int8_linear_path(M, K, N)
+        assert path in (0, 1)
+        if K > 1280:
+            assert path == 0
+        y_auto = tc.int8_linear_tc(xd, wd, sd, bd)
+        y_two = tc.int8_linear_tc(xd, wd, sd, bd, cta_group=1)
+        assert torch.equal(y_auto, y_two)
+    assert tc.device_status() == 0
+
+
+def test_fused_rejects_what_it_cannot_run(tc):
+    x, wq, ws, b = _case(300, 2560, 320, torch.bfloat16, seed=1)
+    with pytest.raises(RuntimeError):
+        tc.int8_linear_tc_fused(x.to(DEV), wq.to(DEV), ws.to(DEV), b.to(DEV))     # K > 1280
+    x, wq, ws, b = _case(300, 48, 320, torch.bfloat16, seed=1)
+    with pytest.raises(RuntimeError):
+        tc.int8_linear_tc_fused(x.to(DEV), wq.to(DEV), ws.to(DEV), b.to(DEV))     # K % 32 != 0
     assert tc.device_status() == 0

@@ -30,7 +30,7 @@ def test_binding_table_covers_header(build_mod):
     declared = set(_declared_symbols())
     bound = set(binding.SIGNATURES) | {"hy3d_arch", "hy3d_status_string",
                                        "hy3d_static_scratch_max_bytes", "hy3d_static_scratch_max_rows",
-                                       "hy3d_fused_sync_bytes"}
+                                       "hy3d_source_digest"}
     assert declared == bound
 
 
@@ -38,7 +38,8 @@ def test_library_identity(build_mod):
     binding = __import__("importlib").import_module("hunyuan3d-tools_b200.csrc._binding")
     lib = binding.configure(build_mod.load_library())
     assert lib.hy3d_arch() == b"sm_100a"
-    assert lib.hy3d_version() >= 100
+    assert lib.hy3d_version() == binding.ABI_VERSION
+    assert lib.hy3d_source_digest().decode() == build_mod._source_digest()
     assert b"alignment" in lib.hy3d_status_string(2)
 
 
@@ -191,3 +192,23 @@ def test_build_digest_does_not_depend_on_the_checkout_location(build_mod, tmp_pa
     copy = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(copy)
     assert copy._source_digest() == build_mod._source_digest()
+
+
+def test_state_dict_in_the_reference_buffer_layout_loads(qu):
+    """A checkpoint that holds only the reference's buffers (weight_int8_nk, weight_scale,
+    bias -- no extra state) loads strictly, also into a layer built without a bias, and a
+    sparse one (compressed buffers filled, dense buffer empty) switches the layer to sparse."""
+    torch.manual_seed(1)
+    src = qu.Int8Linear.from_linear(nn.Linear(128, 64).half())
+    sd = {k: v for k, v in src.state_dict().items() if k != "_extra_state"}
+    assert set(sd) == {"weight_int8_nk", "weight_scale", "bias"}
+    dst = qu.Int8Linear(128, 64, bias=False)
+    dst.load_state_dict(sd, strict=True)
+    assert dst.mode == "tc" and torch.equal(dst.bias, src.bias)
+    assert torch.equal(dst.weight_int8_nk, src.weight_int8_nk)
+    sparse_sd = {"weight_int8_nk": torch.empty(0, dtype=torch.int8), "weight_scale": src.weight_scale,
+                 "weight_sparse_comp": torch.zeros(64, 64, dtype=torch.int8),
+                 "weight_sparse_meta": torch.zeros(64, 4, dtype=torch.int32), "bias": src.bias}
+    dst2 = qu.Int8Linear(128, 64)
+    dst2.load_state_dict(sparse_sd, strict=True)
+    assert dst2.mode == "sparse" and dst2.weight_sparse_comp.shape == (64, 64)

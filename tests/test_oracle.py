@@ -151,3 +151,30 @@ def test_zero_row_and_guard():
     q, s = O.quantize_activation(x)
     assert int(q[0].abs().max()) == 0 and float(s[0]) == pytest.approx(1e-8 / 127.0)
     assert int(q[1, 3]) == 127
+
+
+def test_torch_twin_equals_the_oracle_layer_bit_for_bit():
+    """The torch-op twin used for model-level parity (oracle/torch_twin.py) is a second
+    spelling of linear_w8a8 / linear_w8a8_sparse; anchor it to them: same bits on a dense, a
+    2:4-sparse and a GEGLU layer, 3-D input included."""
+    from types import SimpleNamespace
+    from oracle.torch_twin import OracleInt8Linear
+    M, K, N = 150, 256, 192
+    x, w, b = O.make_case(M, K, N, seed=11, dtype=torch.bfloat16)
+    wq, ws = O.quantize_weight(w)
+    ws16 = ws.bfloat16()
+    dense = SimpleNamespace(in_features=K, out_features=N, mode="tc", epilogue="linear",
+                            weight_int8_nk=wq, weight_scale=ws16, bias=b,
+                            weight_sparse_comp=None, weight_sparse_meta=None)
+    assert torch.equal(OracleInt8Linear(dense)(x), O.linear_w8a8(x, wq, ws16, b))
+    assert torch.equal(OracleInt8Linear(dense)(x.view(3, 50, K)).reshape(M, N), O.linear_w8a8(x, wq, ws16, b))
+    comp, nib = O.prune_compress(wq)
+    sparse = SimpleNamespace(in_features=K, out_features=N, mode="sparse", epilogue="linear",
+                             weight_int8_nk=None, weight_scale=ws16, bias=None,
+                             weight_sparse_comp=comp, weight_sparse_meta=O.pack_metadata(nib, 4 * ((K + 127) // 128)))
+    assert torch.equal(OracleInt8Linear(sparse)(x), O.linear_w8a8_sparse(x, comp, nib, ws16, None))
+    perm = O.geglu_interleave_rows(N)
+    geglu = SimpleNamespace(in_features=K, out_features=N, mode="tc", epilogue="geglu",
+                            weight_int8_nk=wq[perm], weight_scale=ws16[perm], bias=b[perm],
+                            weight_sparse_comp=None, weight_sparse_meta=None)
+    assert torch.equal(OracleInt8Linear(geglu)(x), O.linear_w8a8(x, wq[perm], ws16[perm], b[perm], mode="geglu"))
