@@ -89,14 +89,22 @@ __device__ __forceinline__ uint32_t pack2t(float a, float b) {
 template <bool kBf16, int kEpi>
 __device__ __forceinline__ void slab_math(const uint32_t (&r)[32], float as, const float* wsb,
                                           const float* bsb, uint32_t (&packed)[16]) {
+  // Packed fp32x2 instructions: two IEEE multiplies / fused multiply-adds per issue slot, the
+  // same bits as the scalar forms.
+  const float2 as2 = make_float2(as, as);
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     const float4 w4 = *reinterpret_cast<const float4*>(wsb + 4 * q);
     const float4 b4 = *reinterpret_cast<const float4*>(bsb + 4 * q);
-    float y0 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])), as * w4.x, b4.x);
-    float y1 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 1])), as * w4.y, b4.y);
-    float y2 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])), as * w4.z, b4.z);
-    float y3 = fmaf(static_cast<float>(static_cast<int32_t>(r[4 * q + 3])), as * w4.w, b4.w);
+    const float2 s01 = __fmul2_rn(as2, make_float2(w4.x, w4.y));
+    const float2 s23 = __fmul2_rn(as2, make_float2(w4.z, w4.w));
+    const float2 a01 = make_float2(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])),
+                                   static_cast<float>(static_cast<int32_t>(r[4 * q + 1])));
+    const float2 a23 = make_float2(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])),
+                                   static_cast<float>(static_cast<int32_t>(r[4 * q + 3])));
+    const float2 y01 = __ffma2_rn(a01, s01, make_float2(b4.x, b4.y));
+    const float2 y23 = __ffma2_rn(a23, s23, make_float2(b4.z, b4.w));
+    float y0 = y01.x, y1 = y01.y, y2 = y23.x, y3 = y23.y;
     if (kEpi == HY3D_EPI_GELU) {
       y0 = gelu_erf(y0); y1 = gelu_erf(y1); y2 = gelu_erf(y2); y3 = gelu_erf(y3);
     }

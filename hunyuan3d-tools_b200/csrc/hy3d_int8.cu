@@ -7,3 +7,4 @@
 #include "linear_fused.cu"
 #include "capi.cu"
 #include "static_scratch.cu"
+#include "probes.cu"

@@ -13,12 +13,12 @@
 // use one block, and the rows of the CTA's next block are pulled into L2 ahead of time with a
 // bulk prefetch so the serial quantise phase reads from L2, not from HBM.
 //
-// Roles by warp (576 threads):
+// Roles by warp (832 threads):
 //   warp 0        TMA producer of the weight tiles (block_n rows x 128 B, 128-byte swizzle)
 //   warp 1        tensor-memory owner; one thread issues tcgen05.mma kind::i8
 //   warps 2-9     epilogue, two warps per 32-lane quarter of tensor memory: tcgen05.ld,
 //                 acc * (act_scale[m] * w_scale[n]) + bias[n] (+ GELU / GEGLU), TMA store
-//   warps 10-17   quantiser (16 rows of the block each)
+//   warps 10-25   quantiser (8 rows of the block each)
 // Work is the list of (token block, weight tile) units in token-block-major order; every CTA
 // takes one contiguous range of it, so a block is quantised once per CTA that touches it.
 //
@@ -36,10 +36,12 @@ constexpr int kTileM = 128;
 constexpr int kAtomBytes = kTileM * 128;     // one 128-deep K slice of the token block
 constexpr int kMaxAtoms = 10;                // K <= 1280
 constexpr int kMaxStages = 8;
-constexpr int kEpiWarps = 8;                 // two per 32-lane quarter of tensor memory
-constexpr int kQuantWarps = 8;
-constexpr int kRowsPerQuantWarp = kTileM / kQuantWarps;
-constexpr int kThreads = 64 + 32 * (kEpiWarps + kQuantWarps);
+// 24 worker warps split between the two ALU-heavy roles (template parameter kEW = epilogue
+// warps, a multiple of 4 so that every 32-lane quarter of tensor memory gets the same number):
+// 16 + 8 when a token block feeds many output columns, 8 + 16 when the rows are long.
+constexpr int kWorkerWarps = 24;
+constexpr int kMaxEpiWarps = 16;
+constexpr int kThreads = 64 + 32 * kWorkerWarps;
 constexpr int kSlabCols = 32;                // output columns per TMA store
 constexpr int kSlabBytes = 32 * kSlabCols * 2;
 constexpr int kSmemLimit = 227 * 1024;
@@ -60,6 +62,7 @@ struct FusedArgs {
   int unit_align;         // CTA ranges start at multiples of this many units
   int q_lanes_log2;       // quantiser lanes per row = 1 << q_lanes_log2 (2..5)
   int q_vecs;             // 16-byte vectors per lane and row (<= kMaxVecs)
+  int debug;              // knock-out switches of -DHY3D_TRACE builds (always 0 in the shipped library)
 };
 
 struct __align__(16) FusedCtrl {
@@ -92,10 +95,184 @@ __device__ __forceinline__ void st_shared_v2(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
 
+// 16 accumulator columns of one row -> 16 outputs (rescale, bias, optional GELU, pack) written
+// as two 16-byte pieces into the row's 64-byte line of the staging buffer (64-byte swizzle:
+// 16-byte chunk c of row r sits at c ^ ((r >> 1) & 3)); `hi` selects the line's second half.
 template <bool kBf16, int kEpi>
+__device__ __forceinline__ void chunk_math_store(const uint32_t (&r)[16], float as, const float* wsb,
+                                                 const float* bsb, uint32_t buf_addr, int lane, int hi) {
+  const float2 as2 = make_float2(as, as);
+  uint32_t packed[8];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float4 w4 = *reinterpret_cast<const float4*>(wsb + 4 * q);
+    const float4 b4 = *reinterpret_cast<const float4*>(bsb + 4 * q);
+    const float2 s01 = __fmul2_rn(as2, make_float2(w4.x, w4.y));
+    const float2 s23 = __fmul2_rn(as2, make_float2(w4.z, w4.w));
+    const float2 a01 = make_float2(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])),
+                                   static_cast<float>(static_cast<int32_t>(r[4 * q + 1])));
+    const float2 a23 = make_float2(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])),
+                                   static_cast<float>(static_cast<int32_t>(r[4 * q + 3])));
+    float2 y01 = __ffma2_rn(a01, s01, make_float2(b4.x, b4.y));
+    float2 y23 = __ffma2_rn(a23, s23, make_float2(b4.z, b4.w));
+    if (kEpi == HY3D_EPI_GELU) {
+      y01.x = gelu_erf(y01.x); y01.y = gelu_erf(y01.y); y23.x = gelu_erf(y23.x); y23.y = gelu_erf(y23.y);
+    }
+    packed[2 * q] = dense::pack2t<kBf16>(y01.x, y01.y);
+    packed[2 * q + 1] = dense::pack2t<kBf16>(y23.x, y23.y);
+  }
+  const uint32_t row_addr = buf_addr + static_cast<uint32_t>(lane) * 64u;
+  const uint32_t sw = (static_cast<uint32_t>(lane) >> 1) & 3u;
+  const uint32_t c0 = static_cast<uint32_t>(hi) * 2u;
+  dense::st_shared_v4(row_addr + (((c0) ^ sw) << 4), packed[0], packed[1], packed[2], packed[3]);
+  dense::st_shared_v4(row_addr + (((c0 + 1u) ^ sw) << 4), packed[4], packed[5], packed[6], packed[7]);
+}
+
+struct QuantCtx {
+  uint32_t smem_base, a_block_bytes;
+  int unit_lo, unit_hi, qw, lane;
+  volatile int* abort_flag;
+};
+
+// The quantiser role of one warp: its rows of every token block in the CTA's range, a batch
+// of 32 / G rows at a time (G lanes share a row, each holding kMaxVecs 16-byte vectors), with
+// the loads of the next batch in flight while the current one is reduced, quantised and stored
+// into the swizzled operand tiles.  kLg > 0 fixes G = 1 << kLg with exactly kMaxVecs vectors
+// per lane at compile time (no predicates, store addresses = one base per batch + constants);
+// kLg == 0 reads the geometry from the arguments.
+template <bool kBf16, int kLg, int kRowsPerQuantWarp>
+__device__ __forceinline__ void quantiser_role(const FusedArgs& p, FusedCtrl* ctrl, const QuantCtx& q) {
+  const int lane = q.lane, qw = q.qw;
+  const int lg = kLg > 0 ? kLg : p.q_lanes_log2;
+  const int G = 1 << lg;
+  const int sub = lane & (G - 1);
+  const int rsub = lane >> lg;
+  const int rpb_log2 = 5 - lg;                    // rows per batch = 32 / G
+  constexpr int kRowsLog2 = kRowsPerQuantWarp == 16 ? 4 : 3;
+  static_assert(kRowsPerQuantWarp == (1 << kRowsLog2), "8 or 16 rows per quantiser warp");
+  const int bat_log2 = kRowsLog2 - rpb_log2;      // batches per block = rows per warp / rows per batch
+  const int batches = 1 << bat_log2;
+  const int nvec = p.K >> 3;
+  const int V = kLg > 0 ? kMaxVecs : p.q_vecs;
+  const int m_first = q.unit_lo / p.n_tiles;
+  const int m_last = q.unit_hi > q.unit_lo ? (q.unit_hi - 1) / p.n_tiles : m_first - 1;
+  const int total_batches = (m_last - m_first + 1) << bat_log2;
+  const int row_in_warp0 = qw * kRowsPerQuantWarp + rsub;   // + t * rows_per_batch
+  const uint16_t* lane_src = p.x + static_cast<int64_t>(sub) * 8;
+  HY3D_TRACE_DECL(tr);
+
+  // Pulls this warp's rows of token block m towards L2 (one bulk prefetch per row).
+  auto prefetch_block = [&](int m) {
+    if (m <= m_last && lane < kRowsPerQuantWarp) {
+      const int64_t row = static_cast<int64_t>(m) * kTileM + qw * kRowsPerQuantWarp + lane;
+      if (row < p.M) prefetch_l2_bulk(p.x + row * p.ldx, static_cast<uint32_t>(p.K) * 2u);
+    }
+  };
+  auto load_batch = [&](int idx, uint4 (&v)[kMaxVecs]) {
+    const int m = m_first + (idx >> bat_log2), t = idx & (batches - 1);
+    const int64_t row = static_cast<int64_t>(m) * kTileM + row_in_warp0 + (t << rpb_log2);
+    const bool row_ok = row < p.M;
+    const uint4* src = reinterpret_cast<const uint4*>(lane_src + (row_ok ? row : 0) * p.ldx);
+#pragma unroll
+    for (int i = 0; i < kMaxVecs; ++i) {
+#ifdef HY3D_TRACE
+      if (p.debug & 4) { v[i] = make_uint4(0x3f803f80u, 0x40004000u, 0xbf80bf80u, 0x3f003f00u); continue; }
+#endif
+      if (kLg > 0) v[i] = row_ok ? __ldcs(src + i * G) : make_uint4(0, 0, 0, 0);
+      else v[i] = (i < V && row_ok && sub + i * G < nvec) ? __ldcs(src + i * G) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  // Quantises one batch of rows held in registers into the resident block; false on abort.
+  auto process_batch = [&](int idx, const uint4 (&v)[kMaxVecs]) -> bool {
+    const int blk = idx >> bat_log2, t = idx & (batches - 1);
+    const int m = m_first + blk;
+    const int abuf = blk % p.a_bufs;
+    const int row_local = row_in_warp0 + (t << rpb_log2);
+    const int64_t row = static_cast<int64_t>(m) * kTileM + row_local;
+    const bool row_ok = row < p.M;
+    if (qw == 0 && lane == 0) HY3D_TRACE_FINE(0, tr, 7, idx);
+    uint32_t amax2 = 0;
+#pragma unroll
+    for (int i = 0; i < kMaxVecs; ++i) quant::absmax8<kBf16>(v[i], amax2);
+    float amax = quant::absmax_to_float<kBf16>(amax2);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+      if (off < G) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+    const float inv = __frcp_rn(scale);
+    if (qw == 0 && lane == 0) HY3D_TRACE_FINE(0, tr, 8, idx);
+    if (t == 0) {
+      // The block's shared-memory tiles are free once the MMAs of the block that used them
+      // before have completed.
+      if (qw == 0 && lane == 0) HY3D_TRACE_EVENT(0, tr, 5, blk);
+      if (!mbar_wait(smem_u32(&ctrl->a_empty[abuf]), (static_cast<uint32_t>(blk / p.a_bufs) & 1u) ^ 1u,
+                     q.abort_flag, kDevTimeoutEmpty))
+        return false;
+    }
+    if (sub == 0) {
+      ctrl->as[blk & (kScaleSlots - 1)][row_local] = row_ok ? scale : 0.0f;
+      if (p.scale_out && row_ok) p.scale_out[row] = scale;
+    }
+    const uint32_t row_base = q.smem_base + static_cast<uint32_t>(abuf) * q.a_block_bytes +
+                              static_cast<uint32_t>(row_local) * 128u;
+    const uint32_t sw = static_cast<uint32_t>(row_local) & 7u;
+    const uint32_t sub8 = static_cast<uint32_t>(sub) << 3;
+#pragma unroll
+    for (int i = 0; i < kMaxVecs; ++i) {
+      if (kLg > 0 || (i < V && sub + i * G < nvec)) {
+        float f[8];
+        quant::unpack8<kBf16>(v[i], f);
+        const uint2 c8 = quant::quant8(f, scale, inv);   // rows past M hold zeros: codes 0
+        // byte offset of these 8 codes in the row: sub8 + 8 * G * i; with G fixed the second
+        // term is a constant, so the swizzled address is a per-batch base plus an immediate
+        const uint32_t kc = static_cast<uint32_t>(i * G) << 3;
+        const uint32_t kin = sub8 + (kc & 127u);          // < 256
+        const uint32_t addr = row_base + ((kc >> 7) + (kin >> 7)) * kAtomBytes +
+                              ((((kin & 127u) >> 4) ^ sw) << 4) + (kin & 8u);
+        st_shared_v2(addr, c8.x, c8.y);
+      }
+    }
+    if (qw == 0 && lane == 0) HY3D_TRACE_FINE(0, tr, 9, idx);
+    if (t == batches - 1) {
+      // The tensor core reads these tiles through the async proxy.
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->a_full[abuf]));
+      if (qw == 0 && lane == 0) HY3D_TRACE_EVENT(0, tr, 6, blk);
+      // Every load of this block has been issued.  The first block this warp cannot start
+      // right away (its tiles are still being read by the MMAs) is pulled towards L2 now, so
+      // that HBM keeps streaming while the quantiser waits and the rows are close when the
+      // tiles come free.  Earlier prefetches would only queue ahead of the demand loads.
+#ifdef HY3D_TRACE
+      if (!(p.debug & 8))
+#endif
+      prefetch_block(m + p.a_bufs);
+    }
+    return true;
+  };
+
+  // Software pipeline over (block, batch): the loads of batch i+1 are in flight while batch i
+  // is reduced, quantised and stored.
+  uint4 va[kMaxVecs], vb[kMaxVecs];
+  bool ok = true;
+  if (total_batches > 0) load_batch(0, va);
+  for (int i = 0; ok && i < total_batches; i += 2) {
+    if (i + 1 < total_batches) load_batch(i + 1, vb);
+    ok = process_batch(i, va);
+    if (!ok || i + 1 >= total_batches) break;
+    if (i + 2 < total_batches) load_batch(i + 2, va);
+    ok = process_batch(i + 1, vb);
+  }
+}
+
+template <bool kBf16, int kEpi, int kEW>
 __global__ void __launch_bounds__(kThreads, 1)
 linear_fused_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_o,
                     const FusedArgs p) {
+  constexpr int kEpiWarps = kEW;
+  constexpr int kEpiPerQuarter = kEW / 4;
+  constexpr int kQuantWarps = kWorkerWarps - kEW;
+  constexpr int kRowsPerQuantWarp = kTileM / kQuantWarps;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t smem_base = smem_u32(smem_raw);
@@ -112,7 +289,7 @@ linear_fused_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_const
   float* wsb_all = reinterpret_cast<float*>(smem + staging_off +
                                             static_cast<size_t>(kEpiWarps) * p.store_bufs * kSlabBytes);
   FusedCtrl* ctrl = reinterpret_cast<FusedCtrl*>(reinterpret_cast<uint8_t*>(wsb_all) +
-                                                 kEpiWarps * 128 * sizeof(float));
+                                                 kMaxEpiWarps * 256 * sizeof(float));
   volatile int* abort_flag = &ctrl->abort_flag;
 
   const int warp = threadIdx.x >> 5;
@@ -191,8 +368,9 @@ linear_fused_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_const
           prev_m = m;
           ++blk;
           abuf = blk % p.a_bufs;
-          ok = mbar_wait<true>(smem_u32(&ctrl->a_full[abuf]), static_cast<uint32_t>(blk / p.a_bufs) & 1u,
-                               abort_flag, kDevTimeoutQuant);
+          // a long wait (a whole block is being quantised): park instead of polling
+          ok = mbar_wait(smem_u32(&ctrl->a_full[abuf]), static_cast<uint32_t>(blk / p.a_bufs) & 1u,
+                         abort_flag, kDevTimeoutQuant);
           if (!ok) break;
         }
         const int buf = it & 1;
@@ -240,39 +418,55 @@ linear_fused_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_const
   } else if (warp < 2 + kEpiWarps) {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;            // tensor-memory lane quarter this warp may read
-    const int half = (warp - 2) >> 2;        // which of the two warps sharing that quarter
+    const int half = (warp - 2) >> 2;        // which of the warps sharing that quarter
     const bool geglu = kEpi == HY3D_EPI_GEGLU;
     const int64_t ldo = geglu ? (p.N >> 1) : p.N;
     const uint32_t stage_buf = staging_base + static_cast<uint32_t>((warp - 2) * p.store_bufs) * kSlabBytes;
-    float* wsb = wsb_all + (warp - 2) * 128;   // this warp's copy of the slab's column scales
-    float* bsb = wsb + 64;
-    const int acc_per_slab = geglu ? 2 * kSlabCols : kSlabCols;
-    const int nslab = p.block_n / acc_per_slab;
+    float* wsb = wsb_all + (warp - 2) * 256;   // this warp's column scales (128) and bias (128)
+    float* bsb = wsb + 128;
+    constexpr int kAps = geglu ? 2 * kSlabCols : kSlabCols;   // accumulator columns per slab
+    constexpr int kApsLog2 = geglu ? 6 : 5;
+    const int nslab = p.block_n / kAps;
+    // this warp's slabs: half, half + kEpiPerQuarter, ...
+    const int nmine = nslab > half ? (nslab - half + kEpiPerQuarter - 1) / kEpiPerQuarter : 0;
+    const int ncols = nmine * kAps;                                  // <= 128
     const int pend = p.store_bufs - 1;
-    // Column scale / bias of accumulator column c (fp32), zero outside the matrix.
-    auto col_scale = [&](int n) { return n < p.N ? load_scalar(p.w_scale, p.ws_dtype, n) : 0.0f; };
-    auto col_bias = [&](int n) { return (p.bias && n < p.N) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f; };
     bool ok = true;
     int it = 0, blk = -1, prev_m = -1, sb = 0;
     float as = 0.0f;
+    // Column scales and bias of every slab this warp will take from a tile: fetched one tile
+    // ahead (the loads fly under the previous tile's slabs), staged once per tile.
+    float wv[4], bv[4];
+    auto fetch_cols = [&](int u) {
+      const int n0 = (u % p.n_tiles) * p.block_n;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int idx = lane + 32 * t;
+        const int n = n0 + ((half + kEpiPerQuarter * (idx >> kApsLog2)) << kApsLog2) + (idx & (kAps - 1));
+        const bool in = u < unit_hi && idx < ncols && n < p.N;
+        wv[t] = in ? load_scalar(p.w_scale, p.ws_dtype, n) : 0.0f;
+        bv[t] = (in && p.bias) ? load_scalar(p.bias, p.bias_dtype, n) : 0.0f;
+      }
+    };
+    fetch_cols(unit_lo);
     for (int u = unit_lo; u < unit_hi; ++u, ++it) {
       const int m = u / p.n_tiles;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int m0 = m * kTileM;
       const int n0 = (u - m * p.n_tiles) * p.block_n;
-      // The first slab's column scales are fetched before the accumulators are waited for.
-      float w0 = 0.0f, b0 = 0.0f, w1 = 0.0f, b1 = 0.0f;
-      if (half < nslab) {
-        const int c = n0 + half * acc_per_slab + lane;
-        w0 = col_scale(c); b0 = col_bias(c);
-        if (geglu) { w1 = col_scale(c + 32); b1 = col_bias(c + 32); }
-      }
       if (ok) ok = mbar_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag,
                              kDevTimeoutTmemFull);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = __all_sync(0xffffffffu, ok);   // also: every lane is done with the previous tile's scales
       if (!ok) continue;
       tc_fence_after_sync();
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        wsb[lane + 32 * t] = wv[t];
+        bsb[lane + 32 * t] = bv[t];
+      }
+      __syncwarp();
+      fetch_cols(u + 1);
       if (threadIdx.x == 64) HY3D_TRACE_EVENT(2, tr, 3, u - unit_lo);
       if (m != prev_m) {   // the block's scales were published before its first MMA was issued
         prev_m = m;
@@ -284,31 +478,48 @@ linear_fused_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_const
       const int out_row = m0 + quarter * 32;
       const bool rows_in = out_row < p.M;
       bool arrived = false;
-      for (int s = half; s < nslab; s += 2) {
-        __syncwarp();                       // the previous slab's reads of wsb / bsb are done
-        wsb[lane] = w0; bsb[lane] = b0;
-        if (geglu) { wsb[32 + lane] = w1; bsb[32 + lane] = b1; }
-        __syncwarp();
-        if (s + 2 < nslab) {                // next slab's column scales, one slab ahead
-          const int c = n0 + (s + 2) * acc_per_slab + lane;
-          w0 = col_scale(c); b0 = col_bias(c);
-          if (geglu) { w1 = col_scale(c + 32); b1 = col_bias(c + 32); }
-        }
-        uint32_t packed[16];
-        const bool last = s + 2 >= nslab;
-        if (!geglu) {
-          uint32_t r[32];
-          tmem_ld_x32(t_row + s * kSlabCols, r);
+      if (!geglu) {
+        // 16-column chunks, two per slab; the tensor-memory load of chunk c+1 is in flight
+        // while chunk c is rescaled, packed and written to the staging buffer.
+        const int nchunk = 2 * nmine;
+        uint32_t ra[16], rb[16];
+        auto chunk_col = [&](int c) { return ((half + (c >> 1) * kEpiPerQuarter) << 5) + ((c & 1) << 4); };
+        if (nchunk > 0) tmem_ld_x16(t_row + chunk_col(0), ra);
+        for (int c = 0; c < nchunk; c += 2) {
+          // ---- first half of a slab (registers ra) ----
           tmem_ld_wait();
-          if (last) {
+          tmem_ld_x16(t_row + chunk_col(c + 1), rb);
+          const uint32_t sbuf = stage_buf + sb * kSlabBytes;
+          if (lane == 0) { if (pend) tma_store_wait_read<1>(); else tma_store_wait_read<0>(); }
+          __syncwarp();
+          chunk_math_store<kBf16, kEpi>(ra, as, wsb + (c << 4), bsb + (c << 4), sbuf, lane, 0);
+          // ---- second half (registers rb) ----
+          tmem_ld_wait();
+          if (c + 2 < nchunk) {
+            tmem_ld_x16(t_row + chunk_col(c + 2), ra);
+          } else {
+            // every accumulator column of this warp is in registers: hand the buffer back
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
             arrived = true;
           }
-          dense::slab_math<kBf16, kEpi>(r, as, wsb, bsb, packed);
-        } else {
-          const int c0 = s * acc_per_slab;
+          chunk_math_store<kBf16, kEpi>(rb, as, wsb + (c << 4) + 16, bsb + (c << 4) + 16, sbuf, lane, 1);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int out_col = n0 + chunk_col(c);
+            if (rows_in && out_col < p.N) tma_store_2d(&tm_o, sbuf, out_col * 2, out_row);
+            tma_store_commit();
+          }
+          sb = (sb + 1) & pend;   // store_bufs is 1 or 2
+        }
+      } else {
+        int j = 0;
+        for (int s = half; s < nslab; s += kEpiPerQuarter, ++j) {
+          uint32_t packed[16];
+          const bool last = s + kEpiPerQuarter >= nslab;
+          const int c0 = s * kAps;
 #pragma unroll
           for (int b = 0; b < 2; ++b) {
             uint32_t rv[16], rg[16];
@@ -321,13 +532,14 @@ linear_fused_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_const
               if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[buf]));
               arrived = true;
             }
-            dense::slab_math_geglu<kBf16>(rv, rg, as, wsb + 32 * b, bsb + 32 * b, packed + 8 * b);
+            dense::slab_math_geglu<kBf16>(rv, rg, as, wsb + j * kAps + 32 * b, bsb + j * kAps + 32 * b,
+                                          packed + 8 * b);
           }
+          const int out_col = (n0 + s * kAps) >> 1;
+          dense::slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o, out_col * 2, out_row,
+                            rows_in && out_col < ldo);
+          sb = (sb + 1) & pend;
         }
-        const int out_col = geglu ? ((n0 + s * acc_per_slab) >> 1) : (n0 + s * kSlabCols);
-        dense::slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o, out_col * 2, out_row,
-                          rows_in && out_col < ldo);
-        sb = (sb + 1) % p.store_bufs;
       }
       if (!arrived) {
         tc_fence_before_sync();
@@ -341,106 +553,21 @@ linear_fused_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_const
   } else {
     // ---------------- quantiser ----------------
     const int qw = warp - 2 - kEpiWarps;
-    const int lg = p.q_lanes_log2;
-    const int G = 1 << lg;
-    const int sub = lane & (G - 1);
-    const int rsub = lane >> lg;
-    const int rows_per_batch = 32 >> lg;
-    const int batches = kRowsPerQuantWarp / rows_per_batch;
+    QuantCtx q;
+    q.smem_base = smem_base;
+    q.a_block_bytes = a_block_bytes;
+    q.unit_lo = unit_lo;
+    q.unit_hi = unit_hi;
+    q.qw = qw;
+    q.lane = lane;
+    q.abort_flag = abort_flag;
     const int nvec = p.K >> 3;
-    const int V = p.q_vecs;
-    const int m_first = unit_lo / p.n_tiles;
-    const int m_last = unit_hi > unit_lo ? (unit_hi - 1) / p.n_tiles : m_first - 1;
-    const int total_batches = (m_last - m_first + 1) * batches;
-
-    // Pulls this warp's 16 rows of token block m towards L2 (one bulk prefetch per row).
-    auto prefetch_block = [&](int m) {
-      if (m <= m_last && lane < kRowsPerQuantWarp) {
-        const int64_t row = static_cast<int64_t>(m) * kTileM + qw * kRowsPerQuantWarp + lane;
-        if (row < p.M) prefetch_l2_bulk(p.x + row * p.ldx, static_cast<uint32_t>(p.K) * 2u);
-      }
-    };
-    prefetch_block(m_first);
-    prefetch_block(m_first + 1);
-    auto load_batch = [&](int idx, uint4 (&v)[kMaxVecs]) {
-      const int m = m_first + idx / batches, t = idx % batches;
-      const int64_t row = static_cast<int64_t>(m) * kTileM + qw * kRowsPerQuantWarp +
-                          t * rows_per_batch + rsub;
-      const bool row_ok = row < p.M;
-      const uint4* src = reinterpret_cast<const uint4*>(p.x + (row_ok ? row : 0) * p.ldx);
-#pragma unroll
-      for (int i = 0; i < kMaxVecs; ++i) {
-        const int c = sub + i * G;
-        v[i] = (i < V && row_ok && c < nvec) ? __ldcs(src + c) : make_uint4(0, 0, 0, 0);
-      }
-    };
-    // Quantises one batch of rows held in registers into the resident block; false on abort.
-    auto process_batch = [&](int idx, const uint4 (&v)[kMaxVecs]) -> bool {
-      const int blk = idx / batches, t = idx % batches;
-      const int m = m_first + blk;
-      const int abuf = blk % p.a_bufs;
-      const int row_local = qw * kRowsPerQuantWarp + t * rows_per_batch + rsub;
-      const int64_t row = static_cast<int64_t>(m) * kTileM + row_local;
-      const bool row_ok = row < p.M;
-      uint32_t amax2 = 0;
-#pragma unroll
-      for (int i = 0; i < kMaxVecs; ++i) quant::absmax8<kBf16>(v[i], amax2);
-      float amax = quant::absmax_to_float<kBf16>(amax2);
-      for (int off = G >> 1; off > 0; off >>= 1)
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-      const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
-      const float inv = __frcp_rn(scale);
-      if (t == 0) {
-        // The block's shared-memory tiles are free once the MMAs of the block that used them
-        // before have completed; meanwhile pull the block after next towards L2.
-        prefetch_block(m + 2);
-        if (qw == 0 && lane == 0) HY3D_TRACE_EVENT(0, tr, 5, blk);
-        if (!mbar_wait(smem_u32(&ctrl->a_empty[abuf]), (static_cast<uint32_t>(blk / p.a_bufs) & 1u) ^ 1u,
-                       abort_flag, kDevTimeoutEmpty))
-          return false;
-      }
-      if (sub == 0) {
-        ctrl->as[blk & (kScaleSlots - 1)][row_local] = row_ok ? scale : 0.0f;
-        if (p.scale_out && row_ok) p.scale_out[row] = scale;
-      }
-      const uint32_t row_base = smem_base + static_cast<uint32_t>(abuf) * a_block_bytes +
-                                static_cast<uint32_t>(row_local) * 128u;
-      const uint32_t sw = static_cast<uint32_t>(row_local) & 7u;
-#pragma unroll
-      for (int i = 0; i < kMaxVecs; ++i) {
-        const int c = sub + i * G;          // 8 consecutive K elements
-        if (i < V && c < nvec) {
-          float f[8];
-          quant::unpack8<kBf16>(v[i], f);
-          const uint2 q = quant::quant8(f, scale, inv);   // rows past M hold zeros: codes 0
-          const uint32_t kb = static_cast<uint32_t>(c) << 3;
-          const uint32_t addr = row_base + (kb >> 7) * kAtomBytes +
-                                ((((kb & 127u) >> 4) ^ sw) << 4) + (kb & 8u);
-          st_shared_v2(addr, q.x, q.y);
-        }
-      }
-      if (t == batches - 1) {
-        // The tensor core reads these tiles through the async proxy.
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctrl->a_full[abuf]));
-        if (qw == 0 && lane == 0) HY3D_TRACE_EVENT(0, tr, 6, blk);
-      }
-      return true;
-    };
-
-    // Software pipeline over (block, batch): the loads of batch i+1 are in flight while batch
-    // i is reduced, quantised and stored.
-    uint4 va[kMaxVecs], vb[kMaxVecs];
-    bool ok = true;
-    if (total_batches > 0) load_batch(0, va);
-    for (int i = 0; ok && i < total_batches; i += 2) {
-      if (i + 1 < total_batches) load_batch(i + 1, vb);
-      ok = process_batch(i, va);
-      if (!ok || i + 1 >= total_batches) break;
-      if (i + 2 < total_batches) load_batch(i + 2, va);
-      ok = process_batch(i + 1, vb);
-    }
+    // Rows of 5 x 8, 5 x 16 or 5 x 32 vectors (K = 320, 640, 1280) run with the geometry
+    // fixed at compile time; anything else takes the general loop.
+    if (nvec == 5 * 8) quantiser_role<kBf16, 3, kRowsPerQuantWarp>(p, ctrl, q);
+    else if (nvec == 5 * 16) quantiser_role<kBf16, 4, kRowsPerQuantWarp>(p, ctrl, q);
+    else if (nvec == 5 * 32) quantiser_role<kBf16, 5, kRowsPerQuantWarp>(p, ctrl, q);
+    else quantiser_role<kBf16, 0, kRowsPerQuantWarp>(p, ctrl, q);
     __syncwarp();
   }
 
@@ -464,6 +591,7 @@ linear_fused_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_const
 // Shape of a fused launch; filled by plan_fused.
 struct FusedPlan {
   int block_n, n_tiles, m_blocks, atoms, a_bufs, store_bufs, stages, unit_align, grid, smem_bytes;
+  int epi_warps;   // 8 or 16 of the 24 worker warps
 };
 
 // Whether the resident-block kernel can run this layer at all, and with which tiling.
@@ -480,7 +608,11 @@ int plan_fused(int64_t M, int64_t N, int64_t K, int epilogue, int block_n, int s
   pl.m_blocks = static_cast<int>((M + kTileM - 1) / kTileM);
   pl.atoms = static_cast<int>((K + 127) / 128);
   const int a_bytes = pl.atoms * kAtomBytes;
-  const int fixed0 = static_cast<int>(sizeof(FusedCtrl)) + kEpiWarps * 128 * 4;
+  // The epilogue handles N output columns per token, the quantiser K inputs, at about the
+  // same cost per element: the wider side gets 16 of the 24 worker warps.
+  const int kEpiWarps = (geglu ? N / 2 : N) >= K ? 16 : 8;
+  pl.epi_warps = kEpiWarps;
+  const int fixed0 = static_cast<int>(sizeof(FusedCtrl)) + kMaxEpiWarps * 256 * 4;
   // Shared-memory split for a tile width.  Preference: two resident blocks, then two staging
   // buffers per epilogue warp, as long as at least three weight stages remain; the deepest
   // rows get one block and what is left.
@@ -597,11 +729,15 @@ int linear_fused(const void* x, int x_dtype, int64_t ldx, float* scale_out, cons
   p.unit_align = pl.unit_align;
   // Lanes per row: the power of two (4..32) that leaves at most five 16-byte vectors per lane.
   const int nvec = static_cast<int>(K >> 3);
-  int lg = 2;
+  int lg = 2;   // at most 8 rows per batch, so a batch fits the rows of one quantiser warp
   while (lg < 5 && (nvec + (1 << lg) - 1) / (1 << lg) > kMaxVecs) ++lg;
   p.q_lanes_log2 = lg;
   p.q_vecs = (nvec + (1 << lg) - 1) >> lg;
   if (p.q_vecs > kMaxVecs) return HY3D_ERR_SHAPE;
+  p.debug = 0;
+#ifdef HY3D_TRACE
+  { const char* e = getenv("HY3D_DEBUG"); p.debug = e ? atoi(e) : 0; }
+#endif
 
   const bool geglu = epilogue == HY3D_EPI_GEGLU;
   CUtensorMap tm_b, tm_o;
@@ -613,13 +749,15 @@ int linear_fused(const void* x, int x_dtype, int64_t ldx, float* scale_out, cons
   if (rc != HY3D_OK) return rc;
 
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const FusedArgs);
-  static const KernelFn kernels[2][3] = {
-      {linear_fused_kernel<false, HY3D_EPI_LINEAR>, linear_fused_kernel<false, HY3D_EPI_GELU>,
-       linear_fused_kernel<false, HY3D_EPI_GEGLU>},
-      {linear_fused_kernel<true, HY3D_EPI_LINEAR>, linear_fused_kernel<true, HY3D_EPI_GELU>,
-       linear_fused_kernel<true, HY3D_EPI_GEGLU>}};
+#define HY3D_FUSED_ROW(EW)                                                                            \
+  {{linear_fused_kernel<false, HY3D_EPI_LINEAR, EW>, linear_fused_kernel<false, HY3D_EPI_GELU, EW>,   \
+    linear_fused_kernel<false, HY3D_EPI_GEGLU, EW>},                                                  \
+   {linear_fused_kernel<true, HY3D_EPI_LINEAR, EW>, linear_fused_kernel<true, HY3D_EPI_GELU, EW>,     \
+    linear_fused_kernel<true, HY3D_EPI_GEGLU, EW>}}
+  static const KernelFn kernels[2][2][3] = {HY3D_FUSED_ROW(8), HY3D_FUSED_ROW(16)};
+#undef HY3D_FUSED_ROW
   const int ki = x_dtype == HY3D_BF16 ? 1 : 0;
-  const KernelFn kernel = kernels[ki][epilogue];
+  const KernelFn kernel = kernels[pl.epi_warps == 16 ? 1 : 0][ki][epilogue];
   rc = ensure_max_smem(reinterpret_cast<const void*>(kernel), kSmemLimit);
   if (rc != HY3D_OK) return rc;
   cudaLaunchConfig_t cfg = {};

@@ -30,7 +30,6 @@ def main(argv):
     ws = torch.rand(N, device=dev).bfloat16()
     b = torch.rand(N, device=dev).bfloat16()
     out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-    sync = torch.zeros(int(lib.hy3d_fused_sync_bytes(M)) // 4, dtype=torch.int32, device=dev)
     st = torch.cuda.current_stream().cuda_stream
     if kind == "sparse":
         comp, meta = sp.sparse_prune_and_pack(w)
@@ -51,8 +50,7 @@ def main(argv):
         elif kind == "prune":
             r = lib.hy3d_prune_pack_24(w.data_ptr(), N, K, comp.data_ptr(), None, meta.data_ptr(), ld, st)
         elif kind == "fused":
-            r = lib.hy3d_linear_w8a8_dense_fused(x.data_ptr(), 1, K, q.data_ptr(), s.data_ptr(),
-                                                 sync.data_ptr(), w.data_ptr(), ws.data_ptr(), 1,
+            r = lib.hy3d_linear_w8a8_dense_fused(x.data_ptr(), 1, K, None, w.data_ptr(), ws.data_ptr(), 1,
                                                  b.data_ptr(), 1, out.data_ptr(), 1, M, N, K, 0, 0, st)
         else:
             raise SystemExit(f"unknown kernel kind {kind!r}")

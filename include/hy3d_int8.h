@@ -244,6 +244,19 @@ int hy3d_dequant_bias(const int32_t* acc, const float* act_scale,
 int hy3d_mma_kat(const int8_t* a, const int8_t* b, const uint32_t* meta,
                  int32_t* d, int n, int ksteps, int sparse, void* stream);
 
+/*
+ * Measurement hooks (no reference counterpart; never on the layer path).
+ * hy3d_probe_mma_i8: one CTA per SM issues `groups` groups of four tcgen05.mma kind::i8
+ *   (128 x n x 32, or the 2:4-sparse 128 x n x 64 form when sparse != 0) on operands that stay
+ *   in shared memory, with the commit / wait cadence of a two-stage pipeline and no loads;
+ *   *ops_out receives the dense-equivalent operation count of the launch (2*M*N*K summed), so
+ *   ops / elapsed time is the tensor throughput this GPU sustains for that instruction.
+ * hy3d_probe_hbm: streams `bytes` (a multiple of 16) of the caller's buffer `a` with 16-byte
+ *   accesses from every SM: mode 0 writes it, mode 1 reads it, mode 2 copies it to `b`.
+ */
+int hy3d_probe_mma_i8(int n, int groups, int sparse, int64_t* ops_out, void* stream);
+int hy3d_probe_hbm(int mode, void* a, void* b, int64_t bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
