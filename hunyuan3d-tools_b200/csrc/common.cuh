@@ -128,22 +128,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar, uint32_t cta_r
       ::"r"(bar), "r"(cta_rank)
       : "memory");
 }
-#ifndef HY3D_WAIT_HINT_NS
-#define HY3D_WAIT_HINT_NS 0
-#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-#if HY3D_WAIT_HINT_NS > 0
-  // The thread is suspended until the phase completes or the hinted time has passed, so a
-  // waiting warp takes no issue slots from the warps that have work.
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(HY3D_WAIT_HINT_NS))
-      : "memory");
-#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -151,7 +137,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
-#endif
   return ok != 0;
 }
 // Non-blocking probe.  try_wait may park the thread and was measured to hand control back
@@ -192,14 +177,9 @@ __device__ unsigned long long g_wait_limit_ns = kWaitLimitNs;
 // Bounded wait.  `abort_flag` lives in shared memory and is set by whichever role times
 // out first, so the other roles leave their waits promptly.  Returns false on give-up.
 // kSpin selects test_wait polling (lowest wake-up latency) instead of the parking try_wait.
-template <bool kSpinRequested = false>
+template <bool kSpin = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int err_code) {
-#ifdef HY3D_NO_SPIN
-  constexpr bool kSpin = false;
-#else
-  constexpr bool kSpin = kSpinRequested;
-#endif
   if (kSpin ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
