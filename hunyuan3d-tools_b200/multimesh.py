@@ -111,16 +111,70 @@ class GraphedStep:
         return self.out
 
 
+class GraphedDenoiser:
+    """A whole denoise step -- [x | x] batch, UNet forward, classifier-free guidance, DDIM
+    update -- captured once as a CUDA graph.  A mesh is then ten replays with two small
+    device-to-device copies in between (timestep and coefficients), no host synchronisation
+    and no per-step Python arithmetic on device values."""
+
+    def __init__(self, unet, views: int, size: int, ctx_tokens: int, ctx_dim: int, dtype, device,
+                 steps: int = 10, guidance: float = 3.0):
+        from .unet import ddim_schedule, guided_ddim_update
+        self.steps, self.guidance = steps, guidance
+        self.ts, self.coef_all = ddim_schedule(steps, device)
+        self.x = torch.zeros(views, 4, size, size, dtype=dtype, device=device)
+        self.ctx = torch.zeros(2 * views, ctx_tokens, ctx_dim, dtype=dtype, device=device)
+        self.t = torch.zeros(2 * views, dtype=torch.long, device=device)
+        self.coef = torch.zeros(4, dtype=torch.float32, device=device)
+        self.coef.copy_(self.coef_all[0])
+
+        def one_step():
+            eps = unet(torch.cat([self.x, self.x], dim=0), self.t, self.ctx)
+            return guided_ddim_update(self.x, eps, self.coef, guidance)
+
+        s = torch.cuda.Stream(device=device)
+        s.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(s), torch.no_grad():
+            for _ in range(2):
+                one_step()
+            s.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=s):
+                self.x_next = one_step()
+        torch.cuda.current_stream(device).wait_stream(s)
+
+    @torch.no_grad()
+    def __call__(self, latents, cond, uncond):
+        """Enqueues the whole mesh on the current stream and returns the final latents."""
+        self.x.copy_(latents, non_blocking=True)
+        self.ctx[: uncond.shape[0]].copy_(uncond, non_blocking=True)
+        self.ctx[uncond.shape[0]:].copy_(cond, non_blocking=True)
+        for i in range(self.steps):
+            self.t.copy_(self.ts[i].expand_as(self.t))
+            self.coef.copy_(self.coef_all[i])
+            self.graph.replay()
+            self.x.copy_(self.x_next)
+        return self.x.clone()
+
+
 def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed: int = 0, fuse_geglu=True,
-                       fuse_qkv=True, channels_last=True, verbose=False, **unet_kwargs):
+                       fuse_qkv=True, channels_last=True, verbose=False, init_on_device=False, **unet_kwargs):
     """Random-init UNet of the paint configuration with its Linears swapped for INT8 layers.
     ``quant``: "mixed" (2:4 sparse where K >= 640, dense elsewhere), "dense", "sparse" (the
     reference's sparse mode: small-K layers stay bf16) or "none".  ``fuse_qkv`` stacks the
-    q/k/v (self-attention) and k/v (cross-attention) projections that share an input."""
+    q/k/v (self-attention) and k/v (cross-attention) projections that share an input.
+    ``init_on_device`` draws the random weights on the GPU instead of the CPU."""
     from . import quantize_utils as qu
     from .unet import UNetSD21MV, fuse_geglu_layers, fuse_qkv_layers
     torch.manual_seed(seed)
-    unet = UNetSD21MV(**unet_kwargs).to(dtype).to(device).eval()
+    if init_on_device:
+        # Random initialisation by the device's generator: seconds instead of a minute for the
+        # 0.9 G parameters, same weights on every GPU of the same type for the same seed.
+        with torch.device(device):
+            unet = UNetSD21MV(**unet_kwargs)
+        unet = unet.to(dtype).eval()
+    else:
+        unet = UNetSD21MV(**unet_kwargs).to(dtype).to(device).eval()
     if channels_last:
         unet.use_channels_last()
     stats = {}
@@ -139,18 +193,49 @@ def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed:
     return unet, stats
 
 
+def graphed_denoiser(unet, views: int, size: int, dtype, device, steps: int, guidance: float):
+    """The captured step of ``unet`` for this configuration, built on first use and kept on the
+    model (two eager forwards plus a capture cost as much as a mesh)."""
+    cache = unet.__dict__.setdefault("_graphed_denoisers", {})
+    key = (views, size, dtype, str(device), steps, guidance)
+    if key not in cache:
+        cache[key] = GraphedDenoiser(unet, views, size, 77, 1024, dtype, device, steps, guidance)
+    return cache[key]
+
+
 def denoise_meshes(unet, seeds: Sequence[int], steps: int = 10, guidance: float = 3.0, views: int = 6,
-                   size: int = 64, device="cuda", dtype=torch.bfloat16, graphed: bool = True):
-    """Runs the denoise loop for each seed on this rank; returns (seed -> latents, seconds)."""
+                   size: int = 64, device="cuda", dtype=torch.bfloat16, graphed: bool = True,
+                   inputs: Dict[int, tuple] | None = None):
+    """Runs the denoise loop for each seed on this rank; returns (seed -> latents, seconds of
+    device time measured with CUDA events around the whole loop).  ``inputs`` may hold
+    pre-generated (pinned) host tensors per seed, as a data loader would deliver them; missing
+    ones are generated on the fly."""
     from .unet import denoise
-    step_fn = GraphedStep(unet, 2 * views, size, 77, 1024, dtype, device) if graphed else None
+    den = graphed_denoiser(unet, views, size, dtype, device, steps, guidance) if graphed else None
 
     def one(seed):
-        lat, cond, uncond = mesh_inputs(seed, views, size, dtype=dtype, device=device)
-        return denoise(unet, lat, cond, uncond, steps=steps, guidance=guidance, step_fn=step_fn)
+        if inputs is not None and seed in inputs:
+            lat, cond, uncond = (t.to(device, non_blocking=True) for t in inputs[seed])
+        else:
+            lat, cond, uncond = mesh_inputs(seed, views, size, dtype=dtype, device=device)
+        if den is not None:
+            return den(lat, cond, uncond)
+        return denoise(unet, lat, cond, uncond, steps=steps, guidance=guidance)
 
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(device)
-    t0 = time.perf_counter()
+    e0.record()
     out = run_local(seeds, one)
+    e1.record()
     torch.cuda.synchronize(device)
-    return out, time.perf_counter() - t0
+    return out, e0.elapsed_time(e1) * 1e-3
+
+
+def prefetch_mesh_inputs(seeds: Sequence[int], views: int = 6, size: int = 64, dtype=torch.bfloat16):
+    """Host-side inputs of the given meshes in pinned memory (what a loader thread would have
+    ready before the GPU asks for them)."""
+    out = {}
+    for s in seeds:
+        out[s] = tuple(t.pin_memory() if torch.cuda.is_available() else t
+                       for t in mesh_inputs(s, views, size, dtype=dtype))
+    return out

@@ -291,25 +291,45 @@ def ddim_alphas(num_train_steps=1000, beta_start=0.00085, beta_end=0.012):
     return torch.cumprod(1.0 - betas, dim=0)
 
 
+def ddim_schedule(steps: int, device):
+    """Timesteps and per-step coefficients of the deterministic DDIM update, computed once on
+    the host: ``ts`` (steps,) int64 and ``coef`` (steps, 4) fp32 =
+    [sqrt(1 - a_t), sqrt(a_t), sqrt(a_prev), sqrt(1 - a_prev)], both on ``device``.  Nothing in
+    the step loop has to read a value back from the GPU."""
+    acp = ddim_alphas()
+    ts = torch.linspace(999, 0, steps + 1).long()[:-1]
+    rows = []
+    for i, t in enumerate(ts.tolist()):
+        a_t = acp[t]
+        a_prev = acp[int(ts[i + 1])] if i + 1 < len(ts) else torch.tensor(1.0, dtype=torch.float64)
+        rows.append(torch.stack([(1 - a_t).sqrt(), a_t.sqrt(), a_prev.sqrt(), (1 - a_prev).sqrt()]).float())
+    return ts.to(device), torch.stack(rows).to(device)
+
+
+def guided_ddim_update(x: torch.Tensor, eps: torch.Tensor, coef: torch.Tensor, guidance: float):
+    """Classifier-free guidance on the [uncond | cond] halves of ``eps`` followed by one DDIM
+    update of ``x``; ``coef`` is one row of ``ddim_schedule``.  Pure device arithmetic."""
+    eps_u, eps_c = eps.float().chunk(2, dim=0)
+    e = eps_u + guidance * (eps_c - eps_u)
+    x0 = (x.float() - coef[0] * e) / coef[1]
+    return (coef[2] * x0 + coef[3] * e).to(x.dtype)
+
+
 @torch.no_grad()
 def denoise(unet: UNetSD21MV, latents: torch.Tensor, cond: torch.Tensor, uncond: torch.Tensor,
             steps: int = 10, guidance: float = 3.0, step_fn=None) -> torch.Tensor:
     """latents: (views, 4, H, W) of ONE mesh; cond / uncond: (views, 77, 1024).  Each step runs
     the UNet once on the 2 x views batch [uncond | cond] and applies a deterministic DDIM update
     with guidance scale ``guidance`` (3.0 is the texture pipeline's value).  ``step_fn`` lets a
-    caller substitute a CUDA-graph replay for the eager UNet call."""
-    acp = ddim_alphas().to(latents.device)
-    ts = torch.linspace(999, 0, steps + 1).long()[:-1]
+    caller substitute a CUDA-graph replay for the eager UNet call.  The loop issues device work
+    only: timesteps and coefficients come from ``ddim_schedule``."""
+    ts, coef = ddim_schedule(steps, latents.device)
     context = torch.cat([uncond, cond], dim=0)
     x = latents
-    for i, t in enumerate(ts):
-        t_dev = torch.full((2 * x.shape[0],), int(t), device=x.device, dtype=torch.long)
+    batch = 2 * x.shape[0]
+    for i in range(steps):
+        t_dev = ts[i].expand(batch)
         inp = torch.cat([x, x], dim=0)
         eps = step_fn(inp, t_dev, context) if step_fn is not None else unet(inp, t_dev, context)
-        eps_u, eps_c = eps.float().chunk(2, dim=0)
-        eps = eps_u + guidance * (eps_c - eps_u)
-        a_t = acp[int(t)]
-        a_prev = acp[int(ts[i + 1])] if i + 1 < len(ts) else torch.tensor(1.0, dtype=torch.float64, device=x.device)
-        x0 = (x.float() - (1 - a_t).sqrt().float() * eps) / a_t.sqrt().float()
-        x = (a_prev.sqrt().float() * x0 + (1 - a_prev).sqrt().float() * eps).to(latents.dtype)
+        x = guided_ddim_update(x, eps, coef[i], guidance)
     return x

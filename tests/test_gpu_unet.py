@@ -117,3 +117,16 @@ def test_full_size_unet_ten_steps_matches_oracle_linears():
     b = un.denoise(twin, lat, cond, uncond, steps=10, guidance=3.0)
     assert a.shape == (6, 4, 64, 64) and not torch.isnan(a).any()
     assert O.rel_l2(a, b) < 2e-2
+
+
+def test_graphed_denoiser_equals_eager_loop():
+    """The whole step (batch build, UNet, guidance, DDIM update) captured once and replayed ten
+    times gives the eager loop's latents bit for bit, for two meshes in a row."""
+    mm = importlib.import_module(PKG_NAME + ".multimesh")
+    un = importlib.import_module(PKG_NAME + ".unet")
+    unet, _ = mm.build_texture_unet(DEV, torch.bfloat16, "mixed", seed=1, **SMALL)
+    den = mm.GraphedDenoiser(unet, 2, 16, 7, 128, torch.bfloat16, DEV, steps=10, guidance=3.0)
+    for seed in (5, 6):
+        lat, cond, uncond = mm.mesh_inputs(seed, views=2, size=16, ctx_tokens=7, ctx_dim=128, device=DEV)
+        eager = un.denoise(unet, lat, cond, uncond, steps=10, guidance=3.0)
+        assert torch.equal(den(lat, cond, uncond), eager)
