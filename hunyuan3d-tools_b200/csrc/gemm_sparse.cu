@@ -72,7 +72,9 @@ __device__ __forceinline__ void store_one(void* out, int out_dtype, int64_t idx,
     reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
 }
 
-template <int kG>
+// kBf16 / kEpi select the output packing and the epilogue at compile time for the 16-bit
+// outputs (raw int32 output runs the <false, LINEAR> instance's direct-store path).
+template <int kG, bool kBf16, int kEpi>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_e,
                    const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_o,
@@ -245,8 +247,9 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const int half = (warp - 2) >> 2;               // which of the warps sharing it
     const int row_in_tile = quarter * 32 + lane;    // weight row within the tile
     const int et = threadIdx.x - 64;
-    const bool geglu = p.epilogue == HY3D_EPI_GEGLU;
-    const bool gelu = p.epilogue == HY3D_EPI_GELU;
+    constexpr bool geglu = kEpi == HY3D_EPI_GEGLU;
+    constexpr bool gelu = kEpi == HY3D_EPI_GELU;
+    constexpr int kOutDtype = kBf16 ? HY3D_BF16 : HY3D_F16;
     const int64_t ldo = geglu ? (p.N >> 1) : p.N;
     const uint32_t stage_buf = staging_base + static_cast<uint32_t>(warp - 2) * kSlabBytes;
     bool ok = true;
@@ -318,26 +321,45 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 32; ++j) y[j] = gelu_erf(y[j]);
           }
+          if (geglu) {
+            // Weight rows come in blocks of 32 = 16 value rows then their 16 gate rows: lanes
+            // 0-15 hold the values, lanes 16-31 the matching gates of the same tokens.
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = y[j] * gelu_erf(__shfl_down_sync(0xffffffffu, y[j], 16));
+          }
           if (lane == 0) tma_store_wait_read<0>();
           __syncwarp();
+          if (!geglu) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            // token rows j, j+1 of the slab (64 B each): 16-byte chunk c of row j sits at
-            // c ^ ((j >> 1) & 3), the same for both rows of a pair; one conversion packs both.
-            const uint32_t addr = stage_buf + static_cast<uint32_t>(j) * 64u +
-                                  ((chunk ^ ((static_cast<uint32_t>(j) >> 1) & 3u)) << 4) + in_chunk;
-            const uint32_t pr = pack2(y[j], y[j + 1], p.out_dtype);
-            const uint16_t lo = static_cast<uint16_t>(pr & 0xFFFFu);
-            const uint16_t hi = static_cast<uint16_t>(pr >> 16);
-            asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(lo) : "memory");
-            asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr + 64u), "h"(hi) : "memory");
+            for (int j = 0; j < 32; j += 2) {
+              // token rows j, j+1 of the slab (64 B each): 16-byte chunk c of row j sits at
+              // c ^ ((j >> 1) & 3), the same for both rows of a pair; one conversion packs both.
+              const uint32_t addr = stage_buf + static_cast<uint32_t>(j) * 64u +
+                                    ((chunk ^ ((static_cast<uint32_t>(j) >> 1) & 3u)) << 4) + in_chunk;
+              const uint32_t pr = pack2(y[j], y[j + 1], kOutDtype);
+              const uint16_t lo = static_cast<uint16_t>(pr & 0xFFFFu);
+              const uint16_t hi = static_cast<uint16_t>(pr >> 16);
+              asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(lo) : "memory");
+              asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr + 64u), "h"(hi) : "memory");
+            }
+          } else if (lane < 16) {
+            // 16 output columns per token: plain 32-byte rows (the store's box is 32 B wide)
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const uint32_t addr = stage_buf + static_cast<uint32_t>(j) * 32u + static_cast<uint32_t>(lane) * 2u;
+              const uint32_t pr = pack2(y[j], y[j + 1], kOutDtype);
+              const uint16_t lo = static_cast<uint16_t>(pr & 0xFFFFu);
+              const uint16_t hi = static_cast<uint16_t>(pr >> 16);
+              asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(lo) : "memory");
+              asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr + 32u), "h"(hi) : "memory");
+            }
           }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            const int out_col = w0 + quarter * 32;
+            const int out_col = geglu ? ((w0 + quarter * 32) >> 1) : (w0 + quarter * 32);
             const int out_row = t0 + c0;
-            if (out_col < p.N && out_row < p.M) tma_store_2d(&tm_o, stage_buf, out_col * 2, out_row);
+            if (out_col < ldo && out_row < p.M) tma_store_2d(&tm_o, stage_buf, out_col * 2, out_row);
             tma_store_commit();
           }
         }
@@ -474,7 +496,7 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   const int k_last = static_cast<int>(K - (kblocks - 1) * kBlockK);
   p.last_ksteps = (k_last + 63) / 64;
   const int stage_bytes = kABytes + kEBytes + (block_t / group) * kBlockK;
-  p.tma_store = (out_dtype != HY3D_S32 && epilogue != HY3D_EPI_GEGLU && block_t % kSlabTokens == 0) ? 1 : 0;
+  p.tma_store = (out_dtype != HY3D_S32 && block_t % kSlabTokens == 0) ? 1 : 0;
   const int fixed = static_cast<int>(sizeof(SparseCtrl)) + kEpiWarps * kSlabBytes;
   int stages = (kSmemLimit - fixed) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -497,9 +519,12 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
   if (rc != HY3D_OK) return rc;
 
   if (p.tma_store) {
-    const uint64_t row_bytes = static_cast<uint64_t>(N) * 2;
-    rc = encode_tmap_2d_u8(&tm_o, out, row_bytes, static_cast<uint64_t>(M), row_bytes, 64,
-                           kSlabTokens, 64);
+    // A warp's slab is 32 tokens x 32 weight rows = 64 output bytes per token, or 16 outputs =
+    // 32 bytes per token after the GEGLU gate.
+    const bool geglu = epilogue == HY3D_EPI_GEGLU;
+    const uint64_t row_bytes = static_cast<uint64_t>(geglu ? N / 2 : N) * 2;
+    rc = encode_tmap_2d_u8(&tm_o, out, row_bytes, static_cast<uint64_t>(M), row_bytes, geglu ? 32 : 64,
+                           kSlabTokens, geglu ? 0 : 64);
     if (rc != HY3D_OK) return rc;
   } else {
     tm_o = tm_x;   // unused by the kernel
@@ -507,7 +532,14 @@ int gemm_sparse24(const int8_t* X, const float* act_scale, const int8_t* w_comp,
 
   using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const CUtensorMap, const SparseArgs);
-  const KernelFn kernel = group == 2 ? gemm_sparse_kernel<2> : gemm_sparse_kernel<1>;
+#define HY3D_SPARSE_ROW(G)                                                                                     \
+  {{gemm_sparse_kernel<G, false, HY3D_EPI_LINEAR>, gemm_sparse_kernel<G, false, HY3D_EPI_GELU>,              \
+    gemm_sparse_kernel<G, false, HY3D_EPI_GEGLU>},                                                            \
+   {gemm_sparse_kernel<G, true, HY3D_EPI_LINEAR>, gemm_sparse_kernel<G, true, HY3D_EPI_GELU>,                \
+    gemm_sparse_kernel<G, true, HY3D_EPI_GEGLU>}}
+  static const KernelFn kernels[2][2][3] = {HY3D_SPARSE_ROW(1), HY3D_SPARSE_ROW(2)};
+#undef HY3D_SPARSE_ROW
+  const KernelFn kernel = kernels[group - 1][out_dtype == HY3D_BF16 ? 1 : 0][epilogue];
   rc = ensure_max_smem(reinterpret_cast<const void*>(kernel), kSmemLimit);
   if (rc != HY3D_OK) return rc;
   const int sms = device_sm_count();

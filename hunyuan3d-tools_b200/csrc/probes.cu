@@ -91,11 +91,12 @@ __global__ void __launch_bounds__(512) hbm_stream_kernel(uint4* __restrict__ a, 
     }
     for (; i < nvec; i += stride) __stcs(a + i, v);
   } else if (mode == 1) {
-    for (; i + 3 * stride < nvec; i += 4 * stride) {
-      const uint4 v0 = __ldcs(a + i), v1 = __ldcs(a + i + stride), v2 = __ldcs(a + i + 2 * stride),
-                  v3 = __ldcs(a + i + 3 * stride);
-      acc ^= v0.x ^ v0.y ^ v0.z ^ v0.w ^ v1.x ^ v1.y ^ v1.z ^ v1.w ^ v2.x ^ v2.y ^ v2.z ^ v2.w ^
-             v3.x ^ v3.y ^ v3.z ^ v3.w;
+    for (; i + 7 * stride < nvec; i += 8 * stride) {   // eight 16-byte loads in flight per thread
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __ldcs(a + i + j * stride);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc ^= v[j].x ^ v[j].y ^ v[j].z ^ v[j].w;
     }
     for (; i < nvec; i += stride) { const uint4 v = __ldcs(a + i); acc ^= v.x ^ v.y ^ v.z ^ v.w; }
     if (acc == 0x9E3779B9u) *sink = acc;   // practically never true; defeats dead-code elimination

@@ -158,9 +158,11 @@ class GraphedDenoiser:
 
 
 def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed: int = 0, fuse_geglu=True,
-                       fuse_qkv=True, channels_last=True, verbose=False, init_on_device=False, **unet_kwargs):
+                       fuse_qkv=True, channels_last=True, verbose=False, init_on_device=False,
+                       sparse_min_k=None, **unet_kwargs):
     """Random-init UNet of the paint configuration with its Linears swapped for INT8 layers.
-    ``quant``: "mixed" (2:4 sparse where K >= 640, dense elsewhere), "dense", "sparse" (the
+    ``quant``: "mixed" (2:4 sparse where that kernel is the faster one -- or where
+    K >= ``sparse_min_k`` if given -- dense elsewhere), "dense", "sparse" (the
     reference's sparse mode: small-K layers stay bf16) or "none".  ``fuse_qkv`` stacks the
     q/k/v (self-attention) and k/v (cross-attention) projections that share an input.
     ``init_on_device`` draws the random weights on the GPU instead of the CPU."""
@@ -179,7 +181,7 @@ def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed:
         unet.use_channels_last()
     stats = {}
     if quant == "mixed":
-        stats = qu.quantize_model_mixed(unet, verbose=verbose)
+        stats = qu.quantize_model_mixed(unet, sparse_min_k=sparse_min_k, verbose=verbose)
     elif quant == "dense":
         stats = qu.quantize_model_tensorcore(unet, verbose=verbose)
     elif quant == "sparse":

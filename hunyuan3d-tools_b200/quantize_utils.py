@@ -387,7 +387,7 @@ def quantize_model_sparse(model, min_features=128, sparse_min_k=640, verbose=Tru
     return stats
 
 
-def _replace_linear_sparse(module, min_features, sparse_min_k, stats):
+def _replace_linear_sparse(module, min_features, sparse_min_k, stats, choose=None):
     for name, child in list(module.named_children()):
         if isinstance(child, nn.Linear):
             num_params = child.in_features * child.out_features
@@ -395,7 +395,8 @@ def _replace_linear_sparse(module, min_features, sparse_min_k, stats):
             if child.in_features < min_features or child.out_features < min_features:
                 stats["skipped_params"] += num_params
             elif (child.in_features < sparse_min_k or child.in_features % 64 != 0
-                  or child.out_features % 16 != 0):
+                  or child.out_features % 16 != 0
+                  or (choose is not None and not choose(child.in_features, child.out_features))):
                 stats["kept_fp16"] = stats.get("kept_fp16", 0) + 1
             else:
                 layer = Int8Linear.from_linear_sparse(child)
@@ -405,14 +406,32 @@ def _replace_linear_sparse(module, min_features, sparse_min_k, stats):
                 if layer._sparse_ok:
                     stats["sparse_eligible"] += 1
         else:
-            _replace_linear_sparse(child, min_features, sparse_min_k, stats)
+            _replace_linear_sparse(child, min_features, sparse_min_k, stats, choose)
 
 
-def quantize_model_mixed(model, min_features=128, sparse_min_k=640, verbose=True):
-    """Mixed assignment used by the UNet benchmark: 2:4-sparse layers where K >= sparse_min_k,
-    dense INT8 for every other eligible layer (the reference's sparse mode leaves those in
-    fp16, quantize_utils.py:482-489)."""
-    s1 = quantize_model_sparse(model, min_features, sparse_min_k, verbose=False)
+def sparse_pays(in_features: int, out_features: int) -> bool:
+    """Whether the 2:4-sparse kernel is the faster one for a layer of this size on B200.
+    Measured over the texture UNet's shapes: the sparse GEMM wins where the layer is bound by
+    the tensor pipe and shared-memory bandwidth (deep K and many weight rows -- 1280 -> 10240:
+    34.7 vs 39.1 us, 5120 -> 1280: 15.8 vs 18.7 us at 3072 tokens) and loses where the output
+    write or the per-tile fixed cost dominates (every K <= 640 layer, 1280 -> 320, 1280 -> 1280,
+    2560 -> 640).  The reference used one threshold on K (``sparse_min_k=640``, fitted on an
+    RTX 4090, quantize_utils.py:426)."""
+    return in_features >= 1280 and in_features * out_features >= 5120 * 1280
+
+
+def quantize_model_mixed(model, min_features=128, sparse_min_k=None, verbose=True):
+    """Mixed assignment used by the UNet benchmark: 2:4-sparse layers where that kernel is the
+    faster one (``sparse_pays``, or every K >= ``sparse_min_k`` when a threshold is given, as
+    in the reference's sparse mode), dense INT8 for every other eligible layer (the
+    reference's sparse mode leaves those in fp16, quantize_utils.py:482-489)."""
+    sp_available()
+    s1 = {"total_params": 0, "quantized_params": 0, "skipped_params": 0,
+          "num_replaced": 0, "sparse_eligible": 0, "kept_fp16": 0}
+    if sparse_min_k is not None:
+        _replace_linear_sparse(model, min_features, sparse_min_k, s1)
+    else:
+        _replace_linear_sparse(model, min_features, 0, s1, choose=sparse_pays)
     s2 = quantize_model_tensorcore(model, min_features, verbose=False)
     stats = {"sparse_layers": s1["num_replaced"], "dense_layers": s2["num_replaced"],
              "total_params": s1["total_params"],

@@ -338,3 +338,27 @@ def test_output_canaries_untouched(tc, sp):
     torch.cuda.synchronize()
     assert bool((buf[0] == 0x5A5A5A5A).all()) and bool((buf[M + 1] == 0x5A5A5A5A).all())
     assert torch.equal(buf[1:M + 1].cpu(), O.int32_matmul(A.cpu(), B.cpu()))
+
+
+def test_bounded_wait_gives_up_and_reports(tc):
+    """A device-side wait that can never be satisfied (one thread on a barrier nobody signals,
+    wait limit shortened to 2 ms) ends by itself: the kernel returns, the error word holds the
+    wait's code, the stream check raises with the timeout status, and the next ordinary GEMM on
+    the same context is exact."""
+    lib = tc._lib
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.hy3d_set_wait_limit_ns(2_000_000) == 0
+    try:
+        assert lib.hy3d_wait_selftest(stream) == 0
+        assert lib.hy3d_stream_status(stream) == 5            # HY3D_ERR_TIMEOUT
+        with pytest.raises(RuntimeError, match="timed out"):
+            tc.check_stream()
+        assert tc.device_status() == 0                        # cleared by the raise
+    finally:
+        assert lib.hy3d_set_wait_limit_ns(0) == 0             # back to the default
+    assert lib.hy3d_stream_status(stream) == 0
+    A = torch.randint(-128, 128, (300, 256), dtype=torch.int8)
+    B = torch.randint(-128, 128, (192, 256), dtype=torch.int8)
+    acc = tc.int8_gemm_tc(A.to(DEV), B.to(DEV), None, None, None, out_dtype=torch.int32)
+    assert torch.equal(acc.cpu(), O.int32_matmul(A, B))
+    tc.check_stream()

@@ -148,7 +148,7 @@ def test_geglu_fused_sparse_layer(qu, M):
 def test_mixed_model_surgery(qu):
     torch.manual_seed(4)
     model = nn.Sequential(nn.Linear(320, 1280), nn.Linear(1280, 320), nn.Linear(320, 64)).to(DEV).half()
-    stats = qu.quantize_model_mixed(model, verbose=False)
+    stats = qu.quantize_model_mixed(model, sparse_min_k=640, verbose=False)
     assert stats["sparse_layers"] == 1 and stats["dense_layers"] == 1
     assert model[0].mode == "tc" and model[1].mode == "sparse" and isinstance(model[2], nn.Linear)
     y = model(torch.randn(500, 320, device=DEV, dtype=torch.float16))

@@ -22,7 +22,8 @@ def _twin(unet, qu):
 
 
 SMALL = dict(block_out_channels=(128, 256), attention_heads=(2, 4), cross_attention_dim=128,
-             num_views=2, attn_levels=(True, True))
+             num_views=2, attn_levels=(True, True), sparse_min_k=512)   # threshold rule: the reduced
+# model has no layer large enough for the measured rule, and the sparse kernel must be on the path
 
 
 def test_reduced_unet_ten_steps_matches_oracle_linears():
@@ -92,7 +93,7 @@ def test_full_size_unet_step_runs_and_layer_census():
     with torch.no_grad():
         ref = unet(x, t, ctx)
     stats = qu.quantize_model_mixed(unet, verbose=False)
-    assert stats["num_replaced"] == 280
+    assert stats["num_replaced"] == 280 and stats["sparse_layers"] == 12    # the 1280-level FFN pairs
     with torch.no_grad():
         y = unet(x, t, ctx)
     assert y.shape == (12, 4, 64, 64) and not torch.isnan(y).any()

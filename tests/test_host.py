@@ -212,3 +212,10 @@ def test_state_dict_in_the_reference_buffer_layout_loads(qu):
     dst2 = qu.Int8Linear(128, 64)
     dst2.load_state_dict(sparse_sd, strict=True)
     assert dst2.mode == "sparse" and dst2.weight_sparse_comp.shape == (64, 64)
+
+
+def test_measured_sparse_rule(qu):
+    """Mixed assignment by the measured rule: only deep-K layers with many weight rows."""
+    assert qu.sparse_pays(1280, 10240) and qu.sparse_pays(5120, 1280)
+    for k, n in [(320, 2560), (640, 5120), (1280, 320), (1280, 1280), (2560, 640), (1024, 1280)]:
+        assert not qu.sparse_pays(k, n)
