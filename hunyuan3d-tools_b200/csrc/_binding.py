@@ -29,6 +29,8 @@ _DTYPE_CODE = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32, tor
 SIGNATURES = {
     "hy3d_quantize_rows": [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p],
     "hy3d_quantizer_enum_check": [c_int, c_void_p, c_void_p, c_void_p],
+    "hy3d_layernorm_quantize": [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int,
+                                ctypes.c_float, c_void_p, c_void_p, c_void_p, c_void_p],
     "hy3d_gemm_w8a8_dense": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                              c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int,
                              c_void_p],
@@ -157,6 +159,28 @@ class _Base:
                                                      q.data_ptr(), s.data_ptr(), self._stream(x)),
                         "hy3d_quantize_rows")
         return q, s
+
+    def layernorm_quantize(self, x, gamma, beta, eps, return_normalised=False):
+        """LayerNorm over the last dimension of x (M,K) f16/bf16 fused with the per-token
+        quantiser: returns (int8 (M,K), f32 scale (M)[, normalised activations (M,K)]) equal to
+        quantising the rounded LayerNorm output, without writing that output."""
+        self._req(x, "x", (torch.float16, torch.bfloat16), 2)
+        M, K = x.shape
+        q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+        s = torch.empty((M,), dtype=torch.float32, device=x.device)
+        y = torch.empty_like(x) if return_normalised else None
+        if gamma is not None and beta is not None and gamma.dtype != beta.dtype:
+            beta = beta.to(gamma.dtype)
+        gb = gamma if gamma is not None else beta
+        code = _DTYPE_CODE[gb.dtype] if gb is not None else F32
+        with torch.cuda.device(x.device):
+            self._check(self._lib.hy3d_layernorm_quantize(
+                x.data_ptr(), _DTYPE_CODE[x.dtype], M, K, K,
+                gamma.data_ptr() if gamma is not None else None,
+                beta.data_ptr() if beta is not None else None, code, float(eps),
+                q.data_ptr(), s.data_ptr(), y.data_ptr() if y is not None else None, self._stream(x)),
+                "hy3d_layernorm_quantize")
+        return (q, s, y) if return_normalised else (q, s)
 
     def quantizer_enum_check(self, dtype):
         """(pairs checked, codes differing from rint(x / scale)) over every 16-bit (amax, x)."""

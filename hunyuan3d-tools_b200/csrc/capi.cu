@@ -201,6 +201,15 @@ int hy3d_quantize_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t
   return quantize_rows(x, x_dtype, M, K, ldx, q, scale, static_cast<cudaStream_t>(stream));
 }
 
+int hy3d_layernorm_quantize(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                            const void* gamma, const void* beta, int gb_dtype, float eps, int8_t* q,
+                            float* scale, void* y_out, void* stream) {
+  const int rc = check_device();
+  if (rc != HY3D_OK) return rc;
+  return layernorm_quantize(x, x_dtype, M, K, ldx, gamma, beta, gb_dtype, eps, q, scale, y_out,
+                            static_cast<cudaStream_t>(stream));
+}
+
 int hy3d_quantizer_enum_check(int x_dtype, unsigned long long* pairs_out,
                               unsigned long long* mismatches_out, void* stream) {
   const int rc = check_device();

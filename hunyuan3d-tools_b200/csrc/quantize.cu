@@ -210,6 +210,156 @@ int launch_quantize(const void* x, int64_t M, int64_t K, int64_t ldx, int8_t* q,
   return HY3D_OK;
 }
 
+// LayerNorm fused with the per-token quantiser: the row is normalised in registers, rounded to
+// the 16-bit activation type exactly as a stand-alone LayerNorm would store it, and those
+// rounded values are quantised with the arithmetic above -- so the codes and scales equal
+// quantize_rows(LayerNorm(x)) bit for bit while the normalised activations never go to memory
+// (x is read once: 2*K bytes in, K + 4 bytes out per row, instead of 2K + 2K for the LayerNorm
+// and 2K + K for the quantiser).  Arithmetic, all fp32, fixed reduction order:
+//     mean = sum(x) / K;  var = sum((x - mean)^2) / K;  rstd = 1 / sqrt(var + eps)  (IEEE)
+//     y    = round16( fma((x - mean) * rstd, gamma, beta) )
+// G <= 32 lanes share a row (shuffle reductions); gamma / beta are staged once per block in
+// shared memory as fp32 and the block walks rows with a grid-stride loop.
+template <bool kBf16, int kMaxV>
+__global__ void __launch_bounds__(kQuantThreads)
+layernorm_quantize_kernel(const uint16_t* __restrict__ x, int64_t ldx, const void* __restrict__ gamma,
+                          const void* __restrict__ beta, int gb_dtype, float eps,
+                          int8_t* __restrict__ q, float* __restrict__ scale_out,
+                          uint16_t* __restrict__ y_out, int64_t M, int K, int G) {
+  extern __shared__ float s_gb[];            // gamma[K] then beta[K]
+  pdl_launch_dependents();
+  for (int k = threadIdx.x; k < K; k += blockDim.x) {
+    s_gb[k] = gamma ? load_scalar(gamma, gb_dtype, k) : 1.0f;
+    s_gb[K + k] = beta ? load_scalar(beta, gb_dtype, k) : 0.0f;
+  }
+  pdl_wait();   // x comes from the previous kernel in the stream; gamma / beta are parameters
+  __syncthreads();
+  const int tid = threadIdx.x;
+  const int rows_per_block = kQuantThreads / G;
+  const int sub = tid % G;
+  const int nvec = K >> 3;
+  const float inv_k = 1.0f / static_cast<float>(K);
+  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_block; row0 < M;
+       row0 += static_cast<int64_t>(gridDim.x) * rows_per_block) {
+    const int64_t row = row0 + tid / G;
+    const bool row_ok = row < M;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (row_ok ? row : 0) * ldx);
+    float f[kMaxV][8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int c = sub + i * G;
+      const uint4 v = (row_ok && c < nvec) ? __ldcs(src + c) : make_uint4(0, 0, 0, 0);
+      unpack8<kBf16>(v, f[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum += f[i][j];
+    }
+    for (int off = G >> 1; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float mean = sum * inv_k;
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int c = sub + i * G;
+      if (c < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float d = f[i][j] - mean; ss = fmaf(d, d, ss); }
+      }
+    }
+    for (int off = G >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float rstd = __frcp_rn(__fsqrt_rn(fmaf(ss, inv_k, eps)));
+    // normalise, round to the activation type, keep the rounded values for the quantiser
+    uint32_t amax2 = 0;
+    uint4 yv[kMaxV];
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int c = sub + i * G;
+      yv[i] = make_uint4(0, 0, 0, 0);
+      if (c < nvec) {
+        const float4 g0 = *reinterpret_cast<const float4*>(s_gb + 8 * c);
+        const float4 g1 = *reinterpret_cast<const float4*>(s_gb + 8 * c + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(s_gb + K + 8 * c);
+        const float4 b1 = *reinterpret_cast<const float4*>(s_gb + K + 8 * c + 4);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const float y0 = fmaf((f[i][j] - mean) * rstd, gg[j], bb[j]);
+          const float y1 = fmaf((f[i][j + 1] - mean) * rstd, gg[j + 1], bb[j + 1]);
+          if (kBf16) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
+            w[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+          } else {
+            const __half2 h = __floats2half2_rn(y0, y1);
+            w[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+        }
+        yv[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        absmax8<kBf16>(yv[i], amax2);
+      }
+    }
+    float amax = absmax_to_float<kBf16>(amax2);
+    for (int off = G >> 1; off > 0; off >>= 1)
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+    const float inv = __frcp_rn(scale);
+    if (row_ok && sub == 0) scale_out[row] = scale;
+    uint2* dst = reinterpret_cast<uint2*>(q + (row_ok ? row : 0) * static_cast<int64_t>(K));
+    uint4* ydst = y_out ? reinterpret_cast<uint4*>(y_out + (row_ok ? row : 0) * static_cast<int64_t>(K)) : nullptr;
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      const int c = sub + i * G;
+      if (row_ok && c < nvec) {
+        float fy[8];
+        unpack8<kBf16>(yv[i], fy);
+        dst[c] = quant8(fy, scale, inv);
+        if (ydst) ydst[c] = yv[i];
+      }
+    }
+  }
+}
+
+template <bool kBf16>
+int launch_layernorm_quantize(const void* x, int64_t M, int64_t K, int64_t ldx, const void* gamma,
+                              const void* beta, int gb_dtype, float eps, int8_t* q, float* scale,
+                              void* y_out, cudaStream_t stream) {
+  const int nvec = static_cast<int>(K >> 3);
+  // lanes per row: the power of two (<= 32) that leaves at most 5 vectors per lane
+  int G = 1;
+  while (G < 32 && (nvec + G - 1) / G > 5) G <<= 1;
+  const int maxv = (nvec + G - 1) / G;
+  if (maxv > 8) return HY3D_ERR_SHAPE;
+  const int rows_per_block = kQuantThreads / G;
+  int64_t blocks = (M + rows_per_block - 1) / rows_per_block;
+  const int64_t cap = 148 * 8;
+  if (blocks > cap) blocks = cap;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.blockDim = dim3(kQuantThreads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(2 * K) * sizeof(float);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1] = {pdl_attribute()};
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const uint16_t* xp = reinterpret_cast<const uint16_t*>(x);
+  uint16_t* yp = reinterpret_cast<uint16_t*>(y_out);
+  const int Ki = static_cast<int>(K);
+  cudaError_t err = cudaSuccess;
+#define HY3D_LAUNCH_LNQ(V) \
+  err = cudaLaunchKernelEx(&cfg, layernorm_quantize_kernel<kBf16, V>, xp, ldx, gamma, beta, gb_dtype, eps, \
+                           q, scale, yp, M, Ki, G)
+  if (maxv <= 2) HY3D_LAUNCH_LNQ(2);
+  else if (maxv <= 4) HY3D_LAUNCH_LNQ(4);
+  else if (maxv == 5) HY3D_LAUNCH_LNQ(5);
+  else HY3D_LAUNCH_LNQ(8);
+#undef HY3D_LAUNCH_LNQ
+  if (err != cudaSuccess) {
+    cudaGetLastError();
+    return HY3D_ERR_CUDA;
+  }
+  return HY3D_OK;
+}
+
 // Enumeration behind the quantiser's exactness claim: block a takes the 16-bit pattern a as
 // amax, its threads walk all 65536 patterns x with |x| <= amax and compare the code the
 // quantiser's arithmetic produces with (int8) rint(x / scale) computed by IEEE division.
@@ -292,6 +442,23 @@ int quantize_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
                               : launch_quantize<false>(x, M, K, ldx, q, scale, stream);
 }
 
+int layernorm_quantize(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx, const void* gamma,
+                       const void* beta, int gb_dtype, float eps, int8_t* q, float* scale, void* y_out,
+                       cudaStream_t stream) {
+  if (x_dtype != HY3D_F16 && x_dtype != HY3D_BF16) return HY3D_ERR_ARG;
+  if ((gamma || beta) && (gb_dtype < HY3D_F16 || gb_dtype > HY3D_F32)) return HY3D_ERR_ARG;
+  if (M < 0 || K <= 0 || (K & 7) || K > 2048 || ldx < K || (ldx & 7)) return HY3D_ERR_SHAPE;
+  if (!(eps >= 0.0f)) return HY3D_ERR_ARG;
+  if (M == 0) return HY3D_OK;
+  if (!x || !q || !scale) return HY3D_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7) ||
+      (reinterpret_cast<uintptr_t>(y_out) & 15))
+    return HY3D_ERR_SHAPE;
+  return x_dtype == HY3D_BF16
+             ? launch_layernorm_quantize<true>(x, M, K, ldx, gamma, beta, gb_dtype, eps, q, scale, y_out, stream)
+             : launch_layernorm_quantize<false>(x, M, K, ldx, gamma, beta, gb_dtype, eps, q, scale, y_out, stream);
+}
+
 int quantizer_enum_check(int x_dtype, unsigned long long* pairs, unsigned long long* mismatches,
                          cudaStream_t stream) {
   if (x_dtype != HY3D_F16 && x_dtype != HY3D_BF16) return HY3D_ERR_ARG;
@@ -330,6 +497,7 @@ int dequant_bias(const int32_t* acc, const float* act_scale, const void* w_scale
 }  // namespace quant
 
 using quant::quantize_rows;
+using quant::layernorm_quantize;
 using quant::dequant_bias;
 using quant::quantizer_enum_check;
 

@@ -159,15 +159,16 @@ class GraphedDenoiser:
 
 def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed: int = 0, fuse_geglu=True,
                        fuse_qkv=True, channels_last=True, verbose=False, init_on_device=False,
-                       sparse_min_k=None, **unet_kwargs):
+                       sparse_min_k=None, fuse_ln=True, **unet_kwargs):
     """Random-init UNet of the paint configuration with its Linears swapped for INT8 layers.
     ``quant``: "mixed" (2:4 sparse where that kernel is the faster one -- or where
     K >= ``sparse_min_k`` if given -- dense elsewhere), "dense", "sparse" (the
     reference's sparse mode: small-K layers stay bf16) or "none".  ``fuse_qkv`` stacks the
     q/k/v (self-attention) and k/v (cross-attention) projections that share an input.
-    ``init_on_device`` draws the random weights on the GPU instead of the CPU."""
+    ``init_on_device`` draws the random weights on the GPU instead of the CPU.  ``fuse_ln`` lets
+    the transformer blocks' LayerNorms emit int8 codes for the projections that follow them."""
     from . import quantize_utils as qu
-    from .unet import UNetSD21MV, fuse_geglu_layers, fuse_qkv_layers
+    from .unet import UNetSD21MV, fuse_geglu_layers, fuse_qkv_layers, fuse_layernorm_quant
     torch.manual_seed(seed)
     if init_on_device:
         # Random initialisation by the device's generator: seconds instead of a minute for the
@@ -192,6 +193,8 @@ def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed:
         stats["geglu_fused"] = fuse_geglu_layers(unet)
     if fuse_qkv and quant != "none":
         stats["qkv_layers_removed"] = fuse_qkv_layers(unet)
+    if fuse_ln and quant in ("mixed", "dense"):
+        stats["layernorms_emitting_int8"] = fuse_layernorm_quant(unet)
     return unet, stats
 
 

@@ -95,6 +95,76 @@ def _param_dtype(linear: nn.Linear) -> torch.dtype:
 
 
 # ---------------------------------------------------------------------------------------
+#  Activations that arrive already quantised (emitted by the producing op)
+# ---------------------------------------------------------------------------------------
+class QuantizedActivation:
+    """Per-token int8 codes and scales of an activation tensor, as ``Int8LayerNorm`` emits
+    them, with the logical shape and dtype the unquantised tensor would have had.  An
+    ``Int8Linear`` given one of these skips its own quantise pass and runs the GEMM directly;
+    several sibling layers (q / k / v, the multiview projections, the FFN up-projection) can
+    consume the same object."""
+
+    __slots__ = ("q", "scale", "shape", "dtype")
+
+    def __init__(self, q, scale, shape, dtype):
+        self.q, self.scale, self.shape, self.dtype = q, scale, torch.Size(shape), dtype
+
+    @property
+    def device(self):
+        return self.q.device
+
+    @property
+    def is_cuda(self):
+        return self.q.is_cuda
+
+    def dim(self):
+        return len(self.shape)
+
+    def view(self, *shape):
+        """Re-labels the leading dimensions (tokens stay tokens: the last dimension is fixed)."""
+        shape = tuple(shape[0]) if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)) else shape
+        probe = torch.empty(self.shape, device="meta").view(*shape)
+        if probe.shape[-1] != self.shape[-1]:
+            raise RuntimeError("a quantised activation can only be reshaped over its token dimensions")
+        return QuantizedActivation(self.q, self.scale, probe.shape, self.dtype)
+
+    reshape = view
+
+
+class Int8LayerNorm(nn.Module):
+    """``nn.LayerNorm`` over the last dimension whose output is emitted as int8 codes plus
+    per-token scales (``QuantizedActivation``) by one kernel, so the normalised activations
+    are never written and the consuming ``Int8Linear`` layers do not quantise again.  The codes
+    equal those the consumers would have computed from the rounded LayerNorm output.  Only for
+    LayerNorms whose every consumer is an ``Int8Linear`` (see ``unet.fuse_layernorm_quant``)."""
+
+    def __init__(self, norm: nn.LayerNorm):
+        super().__init__()
+        if len(norm.normalized_shape) != 1:
+            raise RuntimeError("Int8LayerNorm normalises the last dimension only")
+        self.normalized_shape = norm.normalized_shape
+        self.eps = norm.eps
+        self.weight = norm.weight
+        self.bias = norm.bias
+        self._ik = None
+
+    def forward(self, x: torch.Tensor) -> QuantizedActivation:
+        if not x.is_cuda:
+            raise RuntimeError("Int8LayerNorm runs on CUDA tensors only (no CPU fallback)")
+        if self._ik is None:
+            from .csrc.build import load_int8_kernels
+            self._ik = load_int8_kernels()
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        q, s = self._ik.layernorm_quantize(x2, self.weight, self.bias, self.eps)
+        return QuantizedActivation(q, s, x.shape, x.dtype)
+
+    def extra_repr(self) -> str:
+        return f"{self.normalized_shape}, eps={self.eps}, output=int8 codes + per-token scales"
+
+
+# ---------------------------------------------------------------------------------------
 #  Int8Linear
 # ---------------------------------------------------------------------------------------
 class Int8Linear(nn.Module):
@@ -300,7 +370,25 @@ class Int8Linear(nn.Module):
         return self._tc_ref.int8_linear_tc(x, self.weight_int8_nk, self.weight_scale,
                                            self._bias_or_empty(x), _EPILOGUES[self.epilogue])
 
+    def _forward_quantized(self, x: "QuantizedActivation") -> torch.Tensor:
+        """GEMM + epilogue on an activation that was quantised by its producer."""
+        epi = _EPILOGUES[self.epilogue]
+        if self.mode == "sparse":
+            if self._sp_ref is None:
+                self._sp_ref = _load_sp()
+            y = self._sp_ref.sparse_int8_gemm(x.q, x.scale, self.weight_sparse_comp, self.weight_sparse_meta,
+                                              self.weight_scale, self._bias_or_empty(x.q), out_dtype=x.dtype,
+                                              epilogue=epi)
+        else:
+            if self._tc_ref is None:
+                self._tc_ref = _load_tc()
+            y = self._tc_ref.int8_gemm_tc(x.q, self.weight_int8_nk, x.scale, self.weight_scale,
+                                          self._bias_or_empty(x.q), out_dtype=x.dtype, epilogue=epi)
+        return y.reshape(*x.shape[:-1], y.shape[-1])
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if isinstance(x, QuantizedActivation):
+            return self._forward_quantized(x)
         if not x.is_cuda:
             raise RuntimeError("Int8Linear runs on CUDA tensors only (no CPU fallback)")
         if x.dtype not in (torch.float16, torch.bfloat16):

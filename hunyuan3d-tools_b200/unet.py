@@ -259,6 +259,30 @@ def fuse_geglu_layers(model: nn.Module) -> int:
     return n
 
 
+def fuse_layernorm_quant(model: nn.Module) -> int:
+    """Replaces the LayerNorms of every transformer block whose consumers are all
+    ``Int8Linear`` layers by ``Int8LayerNorm``: norm1 -> stacked q/k/v, norm_mv -> stacked
+    multiview q/k/v, norm2 -> cross-attention q, norm3 -> FFN up-projection.  Each of those
+    projections then starts from int8 codes emitted by the normalisation kernel instead of
+    re-reading and re-quantising its bf16 output.  Run after ``fuse_qkv_layers``.  Returns the
+    number of LayerNorms converted."""
+    from .quantize_utils import Int8Linear, Int8LayerNorm
+    n = 0
+    for blk in model.modules():
+        if not isinstance(blk, TransformerBlock):
+            continue
+        pairs = [("norm1", [blk.attn1.to_qkv] if blk.attn1.to_qkv is not None else [blk.attn1.to_q, blk.attn1.to_k, blk.attn1.to_v]),
+                 ("norm_mv", [blk.attn_mv.to_qkv] if blk.attn_mv.to_qkv is not None else [blk.attn_mv.to_q, blk.attn_mv.to_k, blk.attn_mv.to_v]),
+                 ("norm2", [blk.attn2.to_q]),
+                 ("norm3", [blk.ff.proj])]
+        for name, consumers in pairs:
+            norm = getattr(blk, name)
+            if isinstance(norm, nn.LayerNorm) and all(isinstance(c, Int8Linear) for c in consumers):
+                setattr(blk, name, Int8LayerNorm(norm))
+                n += 1
+    return n
+
+
 def fuse_qkv_layers(model: nn.Module) -> int:
     """Stacks the ``Int8Linear`` projections that read the same activation: q/k/v of every
     self-attention into one layer, k/v of every cross-attention into one.  The activation is

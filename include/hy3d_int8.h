@@ -76,6 +76,25 @@ int hy3d_quantize_rows(const void* x, int x_dtype, int64_t M, int64_t K, int64_t
                        int8_t* q, float* scale, void* stream);
 
 /*
+ * LayerNorm over the last dimension fused with the per-token quantiser above: the row is
+ * normalised in registers, rounded to x_dtype exactly as a stand-alone LayerNorm would store
+ * it, and the rounded values are quantised -- q and scale equal
+ * hy3d_quantize_rows(LayerNorm(x)) bit for bit and the normalised activations never go to
+ * memory.  gamma / beta: (K) of gb_dtype (f16/bf16/f32) or NULL (1 / 0).  y_out: optional
+ * (M,K) x_dtype array that receives the rounded LayerNorm output, or NULL.
+ * Arithmetic (fp32): mean = sum(x)/K; var = sum((x-mean)^2)/K; rstd = 1/sqrt(var+eps) with IEEE
+ * square root and reciprocal; y = fma((x-mean)*rstd, gamma, beta).  Requires K % 8 == 0,
+ * K <= 2048, 16-byte aligned rows.
+ * Replaces nothing in the reference by itself: the reference's layers re-quantise the
+ * LayerNorm output for every sibling projection (csrc/int8_sparse_tc.cu:269-271 notes the
+ * re-reads); this is the producer-side emission that removes that pass.  Its consumers are
+ * hy3d_gemm_w8a8_dense / hy3d_gemm_w8a8_sparse24.
+ */
+int hy3d_layernorm_quantize(const void* x, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                            const void* gamma, const void* beta, int gb_dtype, float eps,
+                            int8_t* q, float* scale, void* y_out, void* stream);
+
+/*
  * Self-check of the quantiser's rounding (test hook, no reference counterpart).  The kernel
  * above never divides; this call enumerates on the device every pair of 16-bit patterns
  * (amax, x) of x_dtype with |x| <= amax -- every input the quantiser can meet -- and counts the

@@ -63,6 +63,12 @@ def swap_linears(model: nn.Module, layer_type) -> nn.Module:
         for name, child in list(mod.named_children()):
             if isinstance(child, layer_type):
                 setattr(mod, name, OracleInt8Linear(child))
+            elif type(child).__name__ == "Int8LayerNorm":
+                # a LayerNorm that emits int8 codes: the twin normalises with the plain torch op
+                # and lets the twin layers after it quantise its (rounded) output
+                ln = nn.LayerNorm(child.normalized_shape, eps=child.eps)
+                ln.weight, ln.bias = child.weight, child.bias
+                setattr(mod, name, ln)
             else:
                 swap(child)
     swap(twin)

@@ -362,3 +362,36 @@ def test_bounded_wait_gives_up_and_reports(tc):
     acc = tc.int8_gemm_tc(A.to(DEV), B.to(DEV), None, None, None, out_dtype=torch.int32)
     assert torch.equal(acc.cpu(), O.int32_matmul(A, B))
     tc.check_stream()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K", [(4096, 320), (1000, 640), (333, 1280), (77, 1024), (5, 64), (129, 2048), (2500, 96)])
+def test_layernorm_quantize_equals_quantising_its_own_output(ik, dtype, M, K):
+    """The fused LayerNorm + quantise kernel: (1) its codes and scales are exactly those of the
+    stand-alone quantiser (and of the CPU oracle) applied to the normalised activations it
+    reports; (2) those activations are the fp32 LayerNorm rounded to the activation type, to
+    within a last-place difference of the torch op."""
+    g = torch.Generator().manual_seed(M + K)
+    x = (torch.randn(M, K, generator=g) * 3 + 0.5).to(dtype)
+    gamma = (1 + 0.1 * torch.randn(K, generator=g)).to(dtype)
+    beta = (0.1 * torch.randn(K, generator=g)).to(dtype)
+    q, s, y = ik.layernorm_quantize(x.to(DEV), gamma.to(DEV), beta.to(DEV), 1e-5, return_normalised=True)
+    q2, s2 = ik.fused_quantize_activation(y)
+    assert torch.equal(q, q2) and torch.equal(s, s2)
+    qo, so = O.quantize_activation(y.cpu())
+    assert torch.equal(q.cpu(), qo) and torch.equal(s.cpu(), so)
+    ref = torch.nn.functional.layer_norm(x.float(), (K,), gamma.float(), beta.float(), 1e-5)
+    assert O.rel_l2(y, ref) < (3e-3 if dtype == torch.bfloat16 else 4e-4)       # one output rounding
+    assert float((y.float().cpu() - ref).abs().max()) <= (0.04 if dtype == torch.bfloat16 else 0.005) * float(ref.abs().max())
+    # without the normalised output the codes are the same
+    q3, s3 = ik.layernorm_quantize(x.to(DEV), gamma.to(DEV), beta.to(DEV), 1e-5)
+    assert torch.equal(q3, q) and torch.equal(s3, s)
+
+
+def test_layernorm_quantize_without_affine_and_argument_checks(ik):
+    x = torch.randn(64, 256).bfloat16().to(DEV)
+    q, s, y = ik.layernorm_quantize(x, None, None, 1e-6, return_normalised=True)
+    ref = torch.nn.functional.layer_norm(x.float().cpu(), (256,), None, None, 1e-6)
+    assert O.rel_l2(y, ref) < 3e-3
+    with pytest.raises(RuntimeError):
+        ik.layernorm_quantize(torch.randn(8, 4096).bfloat16().to(DEV), None, None, 1e-5)   # K > 2048

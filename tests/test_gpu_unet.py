@@ -131,3 +131,27 @@ def test_graphed_denoiser_equals_eager_loop():
         lat, cond, uncond = mm.mesh_inputs(seed, views=2, size=16, ctx_tokens=7, ctx_dim=128, device=DEV)
         eager = un.denoise(unet, lat, cond, uncond, steps=10, guidance=3.0)
         assert torch.equal(den(lat, cond, uncond), eager)
+
+
+def test_layernorms_that_emit_int8_keep_the_model_output():
+    """With the transformer blocks' LayerNorms emitting int8 codes for the projections behind
+    them, the UNet output stays within the model-level gate of the model that normalises with
+    the torch op, stores and re-quantises.  (The codes are those of the rounded LayerNorm output;
+    the normalisation's own last-place rounding can differ from the torch op, which flips a few
+    codes and is amplified by the random-init network.)"""
+    mm = importlib.import_module(PKG_NAME + ".multimesh")
+    qu = importlib.import_module(PKG_NAME + ".quantize_utils")
+    a, sa = mm.build_texture_unet(DEV, torch.bfloat16, "mixed", seed=4, fuse_ln=False, **SMALL)
+    b, sb = mm.build_texture_unet(DEV, torch.bfloat16, "mixed", seed=4, fuse_ln=True, **SMALL)
+    n_blocks = sum(1 for m in b.modules() if type(m).__name__ == "TransformerBlock")
+    assert "layernorms_emitting_int8" not in sa and sb["layernorms_emitting_int8"] == 4 * n_blocks
+    assert any(isinstance(m, qu.Int8LayerNorm) for m in b.modules())
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(4, 4, 16, 16, generator=g).bfloat16().to(DEV)
+    ctx = torch.randn(4, 7, 128, generator=g).bfloat16().to(DEV)
+    t = torch.full((4,), 300, device=DEV)
+    with torch.no_grad():
+        ya, yb = a(x, t, ctx), b(x, t, ctx)
+    assert not torch.isnan(yb).any()
+    err = O.rel_l2(yb, ya)
+    assert err < 2e-2, err          # the gate the configuration states for the model's output
