@@ -827,6 +827,10 @@ def run_one_shape(args):
                                             out.data_ptr(), 1, M, N, K, 0, 0, st)
         elif kind == "quant":
             r = lib.hy3d_quantize_rows(x.data_ptr(), 1, M, K, K, q.data_ptr(), s.data_ptr(), st)
+        elif kind == "lnquant":
+            r = lib.hy3d_layernorm_quantize(x.data_ptr(), 1, M, K, K, ws.data_ptr() if N == K else None,
+                                            b.data_ptr() if N == K else None, 1, 1e-5, q.data_ptr(),
+                                            s.data_ptr(), None, st)
         elif kind == "prune":
             r = lib.hy3d_prune_pack_24(w.data_ptr(), N, K, comp.data_ptr(), None, meta.data_ptr(), ld, st)
         elif kind == "fused":
@@ -937,7 +941,7 @@ def main():
                     choices=["dense_sweep", "sparse_sweep", "unet", "multimesh", "one_shape", "ref_kernels"])
     ap.add_argument("--quant", default="mixed", choices=["mixed", "dense", "sparse", "none"])
     ap.add_argument("--quick", action="store_true", help="headline, roofline and e2e only: no sub-records")
-    ap.add_argument("--kernel", default="dense", help="one_shape: dense | sparse | quant | prune | fused")
+    ap.add_argument("--kernel", default="dense", help="one_shape: dense | sparse | quant | lnquant | prune | fused")
     ap.add_argument("--shape", default="8192x1280x1280", help="one_shape: MxKxN")
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--cpu-frac", type=float, default=None,
