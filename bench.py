@@ -758,7 +758,12 @@ def multimesh_record(ctx: Ctx, args):
     seeds = list(range(32))
     mine = mm.partition(seeds, ctx.rank, ctx.world)
     inputs = mm.prefetch_mesh_inputs(mine)
-    mm.denoise_meshes(unet, mine[:1], device=ctx.dev, inputs=inputs)           # warm-up: builds the captured step
+    # warm-up: builds the captured step and the gather's connections (first use of a NCCL
+    # point-to-point path sets up its channels, hundreds of ms that belong to no mesh)
+    warm, _ = mm.denoise_meshes(unet, mine[:1], device=ctx.dev, inputs=inputs)
+    mm.gather_results(warm, [mm.partition(seeds, r, ctx.world)[0] for r in range(ctx.world)],
+                      (6, 4, 64, 64), torch.bfloat16, ctx.dev, dst=0)
+    del warm
     ctx.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -61,6 +61,7 @@ SIGNATURES = {
     "hy3d_wait_selftest": [c_void_p],
     "hy3d_probe_mma_i8": [c_int, c_int, c_int, c_void_p, c_void_p],
     "hy3d_probe_hbm": [c_int, c_void_p, c_void_p, c_int64, c_void_p],
+    "hy3d_probe_tmem_ld": [c_int, c_int, c_int, c_void_p, c_void_p],
     "hy3d_version": [],
 }
 

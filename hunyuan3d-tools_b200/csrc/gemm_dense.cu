@@ -49,6 +49,8 @@ struct DenseArgs {
   int ws_dtype, bias_dtype, out_dtype, epilogue;
   int M, N, K;
   int block_n, stages, acc_cols, tma_store, store_bufs;
+  int b_resident;  // the CTA's B tile (all K blocks) is loaded once and stays in shared memory
+  int wide;    // TMA-store path with 64-column (128-byte) slabs, one per epilogue warp and tile
   int m_tiles, n_tiles, num_kb, last_ksteps, n_fastest;
   int atoms;   // 128-byte K blocks per pipeline stage (1 or 2)
   int debug;   // knock-out switches of -DHY3D_TRACE builds (always 0 in the shipped library)
@@ -61,9 +63,27 @@ struct __align__(16) DenseCtrl {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t b_full;      // resident-B mode: the whole B tile has landed
   uint32_t tmem_base;
   int abort_flag;
 };
+
+// Timeline records of two epilogue warps (the first and the last) in -DHY3D_TRACE builds.
+#ifdef HY3D_TRACE
+#define HY3D_EPI_TRACE(ev, arg)                                              \
+  do {                                                                       \
+    if (threadIdx.x == 64) HY3D_TRACE_EVENT(2, tr, ev, arg);                 \
+    else if (threadIdx.x == kThreads - 32) HY3D_TRACE_EVENT(0, tr, ev, arg); \
+  } while (0)
+#else
+#define HY3D_EPI_TRACE(ev, arg) ((void)0)
+#endif
+
+#ifdef HY3D_KO
+#define HY3D_KO_ARG , p.debug
+#else
+#define HY3D_KO_ARG
+#endif
 
 __device__ __forceinline__ void epi_bar_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
@@ -158,10 +178,60 @@ __device__ __forceinline__ void slab_store(const uint32_t (&packed)[16], uint32_
   }
 }
 
+// 16 accumulator columns of one row -> 16 outputs packed in 8 words, written as two 16-byte
+// pieces (chunks 2k, 2k+1) of the row's 128-byte line in a wide staging buffer (128-byte
+// swizzle: 16-byte chunk c of row r sits at c ^ (r & 7)).
+template <bool kBf16, int kEpi>
+__device__ __forceinline__ void chunk_math_store_wide(const uint32_t (&r)[16], float2 as2,
+                                                      const float* wsb, const float* bsb,
+                                                      uint32_t row_addr, uint32_t sw, uint32_t k,
+                                                      int dbg = 0) {
+  uint32_t packed[8];
+#ifdef HY3D_KO
+  if (dbg & 64) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) packed[j] = r[j] ^ r[j + 8];
+  } else
+#endif
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float4 w4, b4;
+#ifdef HY3D_KO
+    if (dbg & 8) { w4 = make_float4(as2.x, 1.f, as2.x, 2.f); b4 = make_float4(1.f, as2.x, 2.f, as2.x); } else
+#endif
+    {
+      w4 = *reinterpret_cast<const float4*>(wsb + 4 * q);
+      b4 = *reinterpret_cast<const float4*>(bsb + 4 * q);
+    }
+    const float2 s01 = __fmul2_rn(as2, make_float2(w4.x, w4.y));
+    const float2 s23 = __fmul2_rn(as2, make_float2(w4.z, w4.w));
+    const float2 a01 = make_float2(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])),
+                                   static_cast<float>(static_cast<int32_t>(r[4 * q + 1])));
+    const float2 a23 = make_float2(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])),
+                                   static_cast<float>(static_cast<int32_t>(r[4 * q + 3])));
+    float2 y01 = __ffma2_rn(a01, s01, make_float2(b4.x, b4.y));
+    float2 y23 = __ffma2_rn(a23, s23, make_float2(b4.z, b4.w));
+    if (kEpi == HY3D_EPI_GELU) {
+      y01.x = gelu_erf(y01.x); y01.y = gelu_erf(y01.y); y23.x = gelu_erf(y23.x); y23.y = gelu_erf(y23.y);
+    }
+    packed[2 * q] = pack2t<kBf16>(y01.x, y01.y);
+    packed[2 * q + 1] = pack2t<kBf16>(y23.x, y23.y);
+  }
+#ifdef HY3D_KO
+  if (dbg & 16) {
+    if ((packed[0] ^ packed[3] ^ packed[5] ^ packed[7]) == 0x12345678u) st_shared_v4(row_addr, 0, 0, 0, 0);
+    return;
+  }
+#endif
+  st_shared_v4(row_addr + (((2u * k) ^ sw) << 4), packed[0], packed[1], packed[2], packed[3]);
+  st_shared_v4(row_addr + (((2u * k + 1u) ^ sw) << 4), packed[4], packed[5], packed[6], packed[7]);
+}
+
 template <bool kBf16, int kEpi, int kG, int kAtoms>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                  const __grid_constant__ CUtensorMap tm_o, const DenseArgs p) {
+                  const __grid_constant__ CUtensorMap tm_o, const __grid_constant__ CUtensorMap tm_ow,
+                  const DenseArgs p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t smem_base = smem_u32(smem_raw);
@@ -174,9 +244,14 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   // With a CTA pair (kG == 2) each CTA stages its own 128 rows of A and half of the B tile.
   const uint32_t b_bytes = static_cast<uint32_t>(p.block_n / kG) * kBlockKBytes;
   // A stage holds kAtoms 128-byte-wide K blocks of each operand: [A0][A1..][B0][B1..].
-  const uint32_t stage_bytes = static_cast<uint32_t>(kAtoms) * (a_bytes + b_bytes);
-  const uint32_t staging_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
-  DenseCtrl* ctrl = reinterpret_cast<DenseCtrl*>(smem + static_cast<size_t>(p.stages) * stage_bytes +
+  // Resident-B mode (one CTA per tile, one K block per stage): a stage holds A only, and the
+  // CTA's B tile -- it keeps one tile column for the whole launch -- sits behind the ring.
+  const bool b_res = kG == 1 && kAtoms == 1 && p.b_resident;
+  const uint32_t stage_bytes = b_res ? a_bytes : static_cast<uint32_t>(kAtoms) * (a_bytes + b_bytes);
+  const uint32_t b_res_base = smem_base + static_cast<uint32_t>(p.stages) * stage_bytes;
+  const uint32_t b_res_bytes = b_res ? static_cast<uint32_t>(p.num_kb) * b_bytes : 0u;
+  const uint32_t staging_base = b_res_base + b_res_bytes;
+  DenseCtrl* ctrl = reinterpret_cast<DenseCtrl*>(smem + (staging_base - smem_base) +
                                                  kEpiWarps * p.store_bufs * kSlabBytes);
   volatile int* abort_flag = &ctrl->abort_flag;
 
@@ -203,11 +278,13 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       mbar_init(smem_u32(&ctrl->tmem_full[b]), 1);
       mbar_init(smem_u32(&ctrl->tmem_empty[b]), kG * kEpiWarps);   // one arrival per epilogue warp
     }
+    mbar_init(smem_u32(&ctrl->b_full), 1);
     ctrl->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
     if (p.tma_store) tma_prefetch_desc(&tm_o);
+    if (p.wide) tma_prefetch_desc(&tm_ow);
   }
   if (warp == 1) {
     if (kG == 2) {
@@ -235,15 +312,38 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      if (b_res && first_tile < total_tiles) {
+        const uint32_t bf = smem_u32(&ctrl->b_full);
+        const int n0 = tile_n(first_tile) * p.block_n;
+        mbar_arrive_expect_tx(bf, b_res_bytes);
+        for (int kb = 0; kb < p.num_kb; ++kb)
+          tma_load_2d(b_res_base + kb * b_bytes, &tm_b, bf, kb * kBlockKBytes, n0);
+      }
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         const int m0 = tile_m(tile) * (kTileM * kG) + row_off;
         const int n0 = tile_n(tile) * p.block_n + col_off;
         for (int kb = 0; kb < p.num_kb; ++kb) {
+#ifdef HY3D_KO
+          if (p.debug & 256) ok = mbar_wait<true>(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty); else
+#endif
           ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
           if (!ok) break;
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_base + stage * stage_bytes;
-#ifdef HY3D_TRACE
+          if (b_res) {
+            HY3D_TRACE_FINE(3, tr, 20, kb);
+#if defined(HY3D_TRACE) || defined(HY3D_KO)
+            if (p.debug & 1) mbar_arrive(full); else
+#endif
+            {
+            mbar_arrive_expect_tx(full, a_bytes);
+            tma_load_2d(sa, &tm_a, full, kb * kBlockKBytes, m0);
+            }
+            HY3D_TRACE_FINE(3, tr, 21, kb);
+            if (++stage == p.stages) { stage = 0; phase ^= 1; }
+            continue;
+          }
+#if defined(HY3D_TRACE) || defined(HY3D_KO)
           if (p.debug & 1) {
             if (leader) mbar_arrive(full);
           } else
@@ -290,7 +390,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t stage_step = stage_bytes >> 4;
       const uint32_t a_atom = a_bytes >> 4, b_atom = b_bytes >> 4;
       const uint32_t b_off = static_cast<uint32_t>(kAtoms) * a_atom;
-#ifdef HY3D_TRACE
+#if defined(HY3D_TRACE) || defined(HY3D_KO)
       const bool do_mma = !(p.debug & 4);
 #else
       constexpr bool do_mma = true;
@@ -316,9 +416,17 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
         else tc_commit_2cta(smem_u32(&ctrl->empty[stage]), 3);
       };
+      const uint32_t b_res_lo0 = lo_const | ((b_res_base & 0x3FFFFu) >> 4);
+      if (b_res && first_tile < total_tiles) {
+        ok = mbar_wait(smem_u32(&ctrl->b_full), 0, abort_flag, kDevTimeoutFull);
+        tc_fence_after_sync();
+      }
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+#ifdef HY3D_KO
+        if (p.debug & 512) ok = mbar_wait<true>(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag, kDevTimeoutTmemEmpty); else
+#endif
         ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
                        kDevTimeoutTmemEmpty);
         if (!ok) break;
@@ -326,6 +434,31 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         HY3D_TRACE_EVENT(1, tr, 6, it);
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.acc_cols);
         uint32_t acc = 0;   // the first MMA of a tile overwrites the accumulator
+        if (b_res) {
+          // A from the ring, B from its resident block of the same K index.
+          uint32_t xb = b_res_lo0;
+          for (int kb = 0; kb < p.num_kb; ++kb) {
+            ok = wait_full();
+            if (!ok) break;
+            HY3D_TRACE_FINE(1, tr, 22, kb);
+            const int ksteps = kb + 1 < p.num_kb ? 4 : p.last_ksteps;
+            if (do_mma) {
+              for (int k = 0; k < ksteps; ++k) {
+                mma_i8_lohi<kG>(d_tmem, a_lo + 2 * k, xb + 2 * k, desc_hi, idesc, acc);
+                acc = 1u;
+              }
+            }
+            commit_empty();
+            HY3D_TRACE_FINE(1, tr, 23, kb);
+            next_stage();
+            xb += b_atom;
+          }
+          if (ok) {
+            HY3D_TRACE_EVENT(1, tr, 3, it);
+            tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
+          }
+          continue;
+        }
         for (int kb = 0; kb < full_kb; ++kb) {
           ok = wait_full();
           if (!ok) break;
@@ -400,21 +533,30 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // per-column scales / bias are refilled only when the tile column changes (with the grid
     // a multiple of the column count, a CTA keeps its column for the whole launch).
     float as_next = 0.0f;
-    if (scaled && first_tile < total_tiles) {
-      const int m_first = tile_m(first_tile) * (kTileM * kG) + row_off + row_in_tile;
-      if (m_first < p.M) as_next = p.act_scale[m_first];
+    // Tile coordinates advance by additions (tile += tile_step in the walk order), not by a
+    // division per tile: (fast, slow) = (column, row unit) when N-fastest, else the reverse.
+    const int fast_dim = p.n_fastest ? p.n_tiles : p.m_tiles;
+    const int step_slow = tile_step / fast_dim, step_fast = tile_step - step_slow * fast_dim;
+    int t_fast = 0, t_slow = 0;
+    if (first_tile < total_tiles) {
+      t_slow = first_tile / fast_dim;
+      t_fast = first_tile - t_slow * fast_dim;
+      const int m_first = (p.n_fastest ? t_slow : t_fast) * (kTileM * kG) + row_off + row_in_tile;
+      if (scaled && m_first < p.M) as_next = p.act_scale[m_first];
     }
     for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = tile_m(tile) * (kTileM * kG) + row_off;
-      const int n0 = tile_n(tile) * p.block_n;
+      const int m0 = (p.n_fastest ? t_slow : t_fast) * (kTileM * kG) + row_off;
+      const int n0 = (p.n_fastest ? t_fast : t_slow) * p.block_n;
       float as = as_next;
       {
-        const int nt = tile + tile_step;
+        t_fast += step_fast;
+        t_slow += step_slow;
+        if (t_fast >= fast_dim) { t_fast -= fast_dim; ++t_slow; }
         as_next = 0.0f;
-        if (scaled && nt < total_tiles) {
-          const int mn = tile_m(nt) * (kTileM * kG) + row_off + row_in_tile;
+        if (scaled && tile + tile_step < total_tiles) {
+          const int mn = (p.n_fastest ? t_slow : t_fast) * (kTileM * kG) + row_off + row_in_tile;
           if (mn < p.M) as_next = p.act_scale[mn];
         }
       }
@@ -429,6 +571,9 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         cur_n0 = n0;
       }
       const long long w0c = HY3D_CLK();
+#ifdef HY3D_KO
+      if (ok && (p.debug & 1024)) ok = mbar_wait<true>(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag, kDevTimeoutTmemFull); else
+#endif
       if (ok) ok = mbar_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag,
                              kDevTimeoutTmemFull);
       const long long w1c = HY3D_CLK();
@@ -436,7 +581,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) continue;   // warp-uniform; the named barriers above stay balanced
       tc_fence_after_sync();
-      if (threadIdx.x == 64) HY3D_TRACE_EVENT(2, tr, 4, it);
+      HY3D_EPI_TRACE(4, it);
       const int m = m0 + row_in_tile;
       const bool row_ok = m < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
@@ -444,12 +589,67 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const float* wsb = ctrl->ws;
       const float* bsb = ctrl->bs;
       bool arrived = false;
-#ifdef HY3D_TRACE
+#if defined(HY3D_TRACE) || defined(HY3D_KO)
       const bool skip_epilogue = (p.debug & 2) != 0;
 #else
       constexpr bool skip_epilogue = false;
 #endif
-      if (p.tma_store && !skip_epilogue) {
+      if (kEpi != HY3D_EPI_GEGLU && p.wide && !skip_epilogue) {
+        // One slab per warp and tile: warp `half` of a quarter takes the 64 columns
+        // [64*half, 64*half+64) as one 128-byte-wide store, or the 32-column remainder of the
+        // tile as a narrow one.  The accumulator is read in 16-column pieces, the next piece
+        // in flight while the current one is rescaled and staged.
+        const int out_row = m0 + quarter * 32;
+        const bool rows_in = out_row < p.M;
+        const int nwide = p.block_n >> 6;
+        const int c0 = half << 6;
+        const float2 as2 = make_float2(as, as);
+        if (half < nwide) {
+          const uint32_t row_addr = stage_buf + static_cast<uint32_t>(lane) * 128u;
+          const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
+          uint32_t ra[16], rb[16];
+          __syncwarp();
+          tmem_ld_x16(t_row + c0, ra);
+          tmem_ld_wait_for(ra);
+          HY3D_EPI_TRACE(10, it);
+          tmem_ld_x16(t_row + c0 + 16, rb);
+          tma_store_wait_read<0>();   // this warp's previous store has read the buffer
+          __syncwarp();
+          HY3D_EPI_TRACE(11, it);
+          chunk_math_store_wide<kBf16, kEpi>(ra, as2, wsb + c0, bsb + c0, row_addr, sw, 0u HY3D_KO_ARG);
+          tmem_ld_wait_for(rb);
+          tmem_ld_x16(t_row + c0 + 32, ra);
+          chunk_math_store_wide<kBf16, kEpi>(rb, as2, wsb + c0 + 16, bsb + c0 + 16, row_addr, sw, 1u HY3D_KO_ARG);
+          tmem_ld_wait_for(ra);
+          tmem_ld_x16(t_row + c0 + 48, rb);
+          chunk_math_store_wide<kBf16, kEpi>(ra, as2, wsb + c0 + 32, bsb + c0 + 32, row_addr, sw, 2u HY3D_KO_ARG);
+          tmem_ld_wait_for(rb);
+          HY3D_EPI_TRACE(12, it);
+          release_acc(smem_u32(&ctrl->tmem_empty[buf]));
+          arrived = true;
+          chunk_math_store_wide<kBf16, kEpi>(rb, as2, wsb + c0 + 48, bsb + c0 + 48, row_addr, sw, 3u HY3D_KO_ARG);
+          HY3D_EPI_TRACE(13, it);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+#ifdef HY3D_KO
+            if (p.debug & 48) { /* store knocked out */ } else
+#endif
+            if (rows_in && n0 + c0 < p.N) tma_store_2d(&tm_ow, stage_buf, (n0 + c0) * 2, out_row);
+            tma_store_commit();
+          }
+        } else if (half == nwide && (p.block_n & 32)) {
+          uint32_t r[32], packed[16];
+          __syncwarp();
+          tmem_ld_x32(t_row + c0, r);
+          tmem_ld_wait();
+          release_acc(smem_u32(&ctrl->tmem_empty[buf]));
+          arrived = true;
+          slab_math<kBf16, kEpi>(r, as, wsb + c0, bsb + c0, packed);
+          slab_store(packed, stage_buf, lane, 0, &tm_o, (n0 + c0) * 2, out_row,
+                     rows_in && n0 + c0 < p.N);
+        }
+      } else if (p.tma_store && !skip_epilogue) {
         const int nslab = p.block_n / acc_per_slab;
         const int out_row = m0 + quarter * 32;
         const bool rows_in = out_row < p.M;
@@ -471,7 +671,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             slab_math<kBf16, kEpi>(r, as, wsb + s * kSlabCols, bsb + s * kSlabCols, packed);
             slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o,
                        (n0 + s * kSlabCols) * 2, out_row, rows_in && n0 + s * kSlabCols < p.N);
-            sb = (sb + 1) % p.store_bufs;
+            if (++sb == p.store_bufs) sb = 0;
           }
         } else {
           for (int s = half; s < nslab; s += kWarpsPerQuarter) {
@@ -489,7 +689,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             }
             slab_store(packed, stage_buf + sb * kSlabBytes, lane, pend, &tm_o, ((n0 + c0) >> 1) * 2,
                        out_row, rows_in && ((n0 + c0) >> 1) < ldo);
-            sb = (sb + 1) % p.store_bufs;
+            if (++sb == p.store_bufs) sb = 0;
           }
         }
       } else if (p.tma_store) {
@@ -552,7 +752,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           }
         }
       }
-      if (threadIdx.x == 64) HY3D_TRACE_EVENT(2, tr, 5, it);
+      HY3D_EPI_TRACE(5, it);
       acc_tile += HY3D_CLK() - w1c;
       __syncwarp();
       if (!arrived) {
@@ -676,21 +876,70 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   const int k_last = static_cast<int>(K - static_cast<int64_t>(p.num_kb - 1) * stage_k);
   p.last_ksteps = (k_last + 31) / 32;
   p.tma_store = (out_dtype != HY3D_S32 && block_n % (geglu ? 2 * kSlabCols : kSlabCols) == 0) ? 1 : 0;
-  const int stage_bytes = atoms * (kTileM * kBlockKBytes + (block_n / group) * kBlockKBytes);
-  // Two staging buffers per epilogue warp unless that costs one of fewer than four pipeline stages.
-  int store_bufs = 2;
-  {
-    const int fixed2 = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * 2 * kSlabBytes;
-    const int fixed1 = fixed2 - kEpiWarps * kSlabBytes;
+
+  // Grid and tile order.  Tiles are walked N-fastest: CTAs running together share an A tile (a
+  // large activation matrix is then fetched from HBM once, while the small B stays
+  // L2-resident), and with the grid rounded down to a multiple of the column count every CTA
+  // keeps ONE tile column for the whole launch, so its per-column scales and bias are staged
+  // once and the epilogue warps never meet at a CTA-wide barrier again (measured faster or
+  // equal on every sweep shape).
+  const int sms = device_sm_count();
+  if (sms <= 0) return HY3D_ERR_CUDA;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int max_clusters = sms / group;
+  int clusters = total_tiles < max_clusters ? total_tiles : max_clusters;
+  bool column_fixed = p.n_tiles == 1;
+  p.n_fastest = 0;
+  if (p.n_tiles > 1) {
+    p.n_fastest = 1;
+    if (p.n_tiles <= clusters / 4) { clusters -= clusters % p.n_tiles; column_fixed = true; }
+  }
+#ifdef HY3D_TRACE
+  if (const char* e = getenv("HY3D_ORDER")) {
+    p.n_fastest = atoi(e) ? 1 : 0;
+    clusters = total_tiles < max_clusters ? total_tiles : max_clusters;
+    column_fixed = p.n_tiles == 1;
+    if (p.n_fastest && p.n_tiles <= clusters / 4) { clusters -= clusters % p.n_tiles; column_fixed = true; }
+  }
+#endif
+
+  // Shared memory: [pipeline stages][resident B tile][store staging][control block].
+  // A single CTA's load rate from L2 (about 64 bytes per clock) is what paces short-K tiles:
+  // 128 x block_n outputs need (128 + block_n) x K operand bytes per tile.  Where a CTA keeps
+  // its tile column and the column's B tile fits beside at least four A stages, B is loaded
+  // once and only A streams: 128 x K bytes per tile.
+  const int a_stage = kTileM * kBlockKBytes;
+  const int b_tile_bytes = p.num_kb * block_n * kBlockKBytes;
+  const int ctrl_bytes = static_cast<int>(sizeof(DenseCtrl));
+  const int staging1 = kEpiWarps * kSlabBytes;
+  int b_resident = 0, store_bufs = 2, stages = 0, stage_bytes = 0;
+  if (group == 1 && atoms == 1 && column_fixed && total_tiles >= 2 * clusters) {
+    for (int bufs = p.tma_store ? 2 : 1; bufs >= 1 && !b_resident; --bufs) {
+      const int st = (kSmemLimit - ctrl_bytes - bufs * staging1 - b_tile_bytes) / a_stage;
+      if (st >= 4) { b_resident = 1; store_bufs = bufs; stages = st; stage_bytes = a_stage; }
+    }
+  }
+#if defined(HY3D_TRACE) || defined(HY3D_KO)
+  if (const char* e = getenv("HY3D_B_RESIDENT")) { if (!atoi(e)) b_resident = 0; }
+#endif
+  if (!b_resident) {
+    stage_bytes = atoms * (a_stage + (block_n / group) * kBlockKBytes);
+    // Two staging buffers per epilogue warp unless that costs one of fewer than four pipeline stages.
+    store_bufs = 2;
+    const int fixed2 = ctrl_bytes + 2 * staging1, fixed1 = ctrl_bytes + staging1;
     const int stages2 = (kSmemLimit - fixed2) / stage_bytes, stages1 = (kSmemLimit - fixed1) / stage_bytes;
     if (stages2 < 4 && stages1 > stages2) store_bufs = 1;
 #ifdef HY3D_TRACE
     if (const char* e = getenv("HY3D_STORE_BUFS")) store_bufs = atoi(e) == 1 ? 1 : 2;
 #endif
+    stages = (kSmemLimit - ctrl_bytes - store_bufs * staging1) / stage_bytes;
   }
+  p.b_resident = b_resident;
   p.store_bufs = store_bufs;
-  const int fixed = static_cast<int>(sizeof(DenseCtrl)) + kEpiWarps * store_bufs * kSlabBytes;
-  int stages = (kSmemLimit - fixed) / stage_bytes;
+  // Wide (128-byte) store slabs need the 4 KB of two narrow buffers per warp and at least three
+  // slabs per quarter to keep three of its four warps busy; narrower tiles keep 32-column slabs.
+  p.wide = (p.tma_store && !geglu && store_bufs == 2 && block_n >= 160) ? 1 : 0;
+  const int fixed = ctrl_bytes + store_bufs * staging1 + (b_resident ? b_tile_bytes : 0);
   if (stages > kMaxStages) stages = kMaxStages;
 #ifdef HY3D_TRACE
   if (const char* e = getenv("HY3D_STAGES")) { const int v = atoi(e); if (v >= 2 && v < stages) stages = v; }
@@ -698,12 +947,12 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   if (stages < 2) return HY3D_ERR_SHAPE;
   p.stages = stages;
   p.debug = 0;
-#ifdef HY3D_TRACE
+#if defined(HY3D_TRACE) || defined(HY3D_KO)
   { const char* e = getenv("HY3D_DEBUG"); p.debug = e ? atoi(e) : 0; }
 #endif
   const int smem_bytes = stages * stage_bytes + fixed;
 
-  CUtensorMap tm_a, tm_b, tm_o;
+  CUtensorMap tm_a, tm_b, tm_o, tm_ow;
   int rc = encode_tmap_2d_u8(&tm_a, A, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
                              static_cast<uint64_t>(K), kBlockKBytes, kTileM, 128);
   if (rc != HY3D_OK) return rc;
@@ -719,8 +968,16 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   } else {
     tm_o = tm_a;   // unused by the kernel
   }
+  if (p.wide) {
+    const uint64_t row_bytes = static_cast<uint64_t>(N) * 2;
+    rc = encode_tmap_2d_u8(&tm_ow, out, row_bytes, static_cast<uint64_t>(M), row_bytes, 128, 32, 128);
+    if (rc != HY3D_OK) return rc;
+  } else {
+    tm_ow = tm_a;  // unused by the kernel
+  }
 
-  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const DenseArgs);
+  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                            const DenseArgs);
   // [0]: one CTA per tile, [1]: CTA pairs, [2]: CTA pairs with deep (two-block) stages.
 #define HY3D_DENSE_ROW(G, A)                                                              \
   {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, G, A>, gemm_dense_kernel<false, HY3D_EPI_GELU, G, A>, \
@@ -735,28 +992,6 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   const KernelFn kernel = kernels[variant][ki][epilogue];
   rc = ensure_max_smem(reinterpret_cast<const void*>(kernel), kSmemLimit);
   if (rc != HY3D_OK) return rc;
-  const int sms = device_sm_count();
-  if (sms <= 0) return HY3D_ERR_CUDA;
-  const int total_tiles = p.m_tiles * p.n_tiles;
-  const int max_clusters = sms / group;
-  int clusters = total_tiles < max_clusters ? total_tiles : max_clusters;
-  // Tiles are walked N-fastest: CTAs running together share an A tile (a large activation
-  // matrix is then fetched from HBM once, while the small B stays L2-resident), and with the
-  // grid rounded down to a multiple of the column count every CTA keeps ONE tile column for
-  // the whole launch, so its per-column scales and bias are staged once and the epilogue warps
-  // never meet at a CTA-wide barrier again (measured faster or equal on every sweep shape).
-  p.n_fastest = 0;
-  if (p.n_tiles > 1) {
-    p.n_fastest = 1;
-    if (p.n_tiles <= clusters / 4) clusters -= clusters % p.n_tiles;
-  }
-#ifdef HY3D_TRACE
-  if (const char* e = getenv("HY3D_ORDER")) {
-    p.n_fastest = atoi(e) ? 1 : 0;
-    clusters = total_tiles < max_clusters ? total_tiles : max_clusters;
-    if (p.n_fastest && p.n_tiles <= clusters / 4) clusters -= clusters % p.n_tiles;
-  }
-#endif
   const int grid = group * clusters;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -771,7 +1006,7 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  if (cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_o, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_o, tm_ow, p) != cudaSuccess) {
     cudaGetLastError();
     return HY3D_ERR_CUDA;
   }

@@ -4,6 +4,8 @@
 //   hy3d_probe_mma_i8   resident-operand tcgen05.mma kind::i8 issue loop on every SM: the
 //                       practical INT8 tensor peak (dense or 2:4 sparse) under the power cap
 //   hy3d_probe_hbm      write-only / read-only / copy streams over a caller-provided buffer
+//   hy3d_probe_tmem_ld  tensor-memory -> register drain rate (tcgen05.ld 32x32b.x16) with a
+//                       chosen number of warps and loads in flight per warp
 #include "common.cuh"
 
 namespace hy3d {
@@ -112,6 +114,41 @@ __global__ void __launch_bounds__(512) hbm_stream_kernel(uint4* __restrict__ a, 
 
 __device__ uint32_t g_probe_sink;
 
+// One CTA per SM, `blockDim.x / 32` warps.  Every warp reads its lane quarter of tensor memory
+// `iters` times: kDepth loads of 16 columns are issued back to back, then one wait.
+template <int kDepth>
+__global__ void __launch_bounds__(512, 1) tmem_drain_kernel(int iters, uint32_t* sink) {
+  __shared__ uint32_t tmem_base_s;
+  const int warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    tmem_alloc_1cta(smem_u32(&tmem_base_s), 512);
+    tmem_relinquish_1cta();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t t_row = tmem_base_s + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+  uint32_t acc = 0;
+  uint32_t col = static_cast<uint32_t>(warp >> 2) * 64u;
+  for (int i = 0; i < iters; ++i) {
+    uint32_t r[kDepth][16];
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) tmem_ld_x16(t_row + ((col + 16u * d) & 511u), r[d]);
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) tmem_ld_wait_for(r[d]);
+#pragma unroll
+    for (int d = 0; d < kDepth; ++d) acc ^= r[d][0] ^ r[d][7] ^ r[d][15];
+    col = (col + 16u * kDepth) & 511u;
+  }
+  if (acc == 0x9E3779B9u) *sink = acc;
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc_1cta(tmem_base_s, 512);
+  }
+}
+
 }  // namespace
 }  // namespace probe
 }  // namespace hy3d
@@ -133,6 +170,23 @@ int hy3d_probe_mma_i8(int n, int groups, int sparse, int64_t* ops_out, void* str
   // Dense-equivalent operations of the launch: a sparse instruction covers 64 logical K.
   if (ops_out)
     *ops_out = static_cast<int64_t>(sms) * groups * 4 * 2 * 128 * n * (sparse ? 64 : 32);
+  return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
+}
+
+int hy3d_probe_tmem_ld(int warps, int depth, int iters, int64_t* bytes_out, void* stream) {
+  using namespace hy3d;
+  if (warps < 4 || warps > 16 || (warps & 3) || iters < 1 || iters > (1 << 24)) return HY3D_ERR_ARG;
+  if (depth != 1 && depth != 2 && depth != 4) return HY3D_ERR_ARG;
+  const int sms = device_sm_count();
+  if (sms <= 0) return HY3D_ERR_CUDA;
+  uint32_t* sink = nullptr;
+  if (cudaGetSymbolAddress(reinterpret_cast<void**>(&sink), probe::g_probe_sink) != cudaSuccess)
+    return HY3D_ERR_CUDA;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (depth == 1) probe::tmem_drain_kernel<1><<<sms, warps * 32, 0, s>>>(iters, sink);
+  else if (depth == 2) probe::tmem_drain_kernel<2><<<sms, warps * 32, 0, s>>>(iters, sink);
+  else probe::tmem_drain_kernel<4><<<sms, warps * 32, 0, s>>>(iters, sink);
+  if (bytes_out) *bytes_out = static_cast<int64_t>(sms) * warps * iters * depth * 2048;
   return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
 }
 

@@ -276,6 +276,14 @@ int hy3d_mma_kat(const int8_t* a, const int8_t* b, const uint32_t* meta,
 int hy3d_probe_mma_i8(int n, int groups, int sparse, int64_t* ops_out, void* stream);
 int hy3d_probe_hbm(int mode, void* a, void* b, int64_t bytes, void* stream);
 
+/*
+ * Tensor-memory drain rate (measurement hook, no reference counterpart): one CTA per SM with
+ * `warps` warps (4, 8, 12 or 16), each reading its 32-lane quarter `iters` times with `depth`
+ * (1, 2 or 4) tcgen05.ld 32x32b.x16 loads in flight before one wait.  *bytes_out receives the
+ * bytes the launch moved from tensor memory to registers; the caller times the launch.
+ */
+int hy3d_probe_tmem_ld(int warps, int depth, int iters, int64_t* bytes_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
