@@ -255,7 +255,11 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                                                  kEpiWarps * p.store_bufs * kSlabBytes);
   volatile int* abort_flag = &ctrl->abort_flag;
 
-  const int warp = threadIdx.x >> 5;
+  // The warp index comes through a shuffle so that the compiler knows it is the same for the
+  // whole warp: the producer and MMA roles below then run as warp-uniform loops (all 32 lanes
+  // wait and count, one lane issues), and their descriptors, coordinates and barrier
+  // addresses can live in uniform registers instead of being converted for every issue.
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const int total_tiles = p.m_tiles * p.n_tiles;     // m_tiles counts 128*kG-row units
   const uint32_t cta_rank = kG == 2 ? cluster_cta_rank() : 0u;
@@ -307,18 +311,20 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   pdl_wait();
 
   if (warp == 0) {
-    // ---------------- TMA producer (one thread) ----------------
-    if (lane == 0) {
+    // ---------------- TMA producer (all lanes walk the loop, lane 0 issues) ----------------
+    {
+      const bool issuer = lane == 0;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      if (b_res && first_tile < total_tiles) {
+      if (b_res && first_tile < total_tiles && issuer) {
         const uint32_t bf = smem_u32(&ctrl->b_full);
         const int n0 = tile_n(first_tile) * p.block_n;
         mbar_arrive_expect_tx(bf, b_res_bytes);
         for (int kb = 0; kb < p.num_kb; ++kb)
           tma_load_2d(b_res_base + kb * b_bytes, &tm_b, bf, kb * kBlockKBytes, n0);
       }
+      __syncwarp();
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
         const int m0 = tile_m(tile) * (kTileM * kG) + row_off;
         const int n0 = tile_n(tile) * p.block_n + col_off;
@@ -327,17 +333,18 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if (p.debug & 256) ok = mbar_wait<true>(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty); else
 #endif
           ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_base + stage * stage_bytes;
           if (b_res) {
             HY3D_TRACE_FINE(3, tr, 20, kb);
 #if defined(HY3D_TRACE) || defined(HY3D_KO)
-            if (p.debug & 1) mbar_arrive(full); else
+            if (p.debug & 1) { if (issuer) mbar_arrive(full); } else
 #endif
-            {
-            mbar_arrive_expect_tx(full, a_bytes);
-            tma_load_2d(sa, &tm_a, full, kb * kBlockKBytes, m0);
+            if (issuer) {
+              mbar_arrive_expect_tx(full, a_bytes);
+              tma_load_2d(sa, &tm_a, full, kb * kBlockKBytes, m0);
             }
             HY3D_TRACE_FINE(3, tr, 21, kb);
             if (++stage == p.stages) { stage = 0; phase ^= 1; }
@@ -345,10 +352,12 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           }
 #if defined(HY3D_TRACE) || defined(HY3D_KO)
           if (p.debug & 1) {
-            if (leader) mbar_arrive(full);
+            if (leader && issuer) mbar_arrive(full);
           } else
 #endif
-          if (kG == 1) {
+          if (!issuer) {
+            // only lane 0 issues
+          } else if (kG == 1) {
             mbar_arrive_expect_tx(full, stage_bytes);
 #pragma unroll
             for (int a = 0; a < kAtoms; ++a) {
@@ -377,7 +386,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     // The tensor pipe accepts an MMA only when it can start it, so every cycle this thread
     // spends between two issues is a cycle the pipe idles: the loop is kept to one barrier
     // probe, four issues and one commit per stage.
-    if (lane == 0 && leader) {
+    if (leader) {
+      const bool issuer = lane == 0;
       const uint32_t idesc = make_idesc_i8(kTileM * kG, static_cast<uint32_t>(p.block_n), false);
       // Descriptor = (low word: address field + leading-dimension offset, high word: stride,
       // version, swizzle).  Only the 14-bit address field changes from stage to stage and from
@@ -408,8 +418,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       };
       auto wait_full = [&]() {
         const uint32_t bar = smem_u32(&ctrl->full[stage]);
-        if (mbar_test_wait(bar, phase)) return true;
-        return mbar_wait<true>(bar, phase, abort_flag, kDevTimeoutFull);
+        bool r = mbar_test_wait(bar, phase);
+        if (__all_sync(0xffffffffu, r)) return true;
+        if (!r) r = mbar_wait<true>(bar, phase, abort_flag, kDevTimeoutFull);
+        return __all_sync(0xffffffffu, r) != 0;
       };
       auto commit_empty = [&]() {
         // Frees the stage (in both CTAs of a pair) once these MMAs have read it.
@@ -419,6 +431,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       const uint32_t b_res_lo0 = lo_const | ((b_res_base & 0x3FFFFu) >> 4);
       if (b_res && first_tile < total_tiles) {
         ok = mbar_wait(smem_u32(&ctrl->b_full), 0, abort_flag, kDevTimeoutFull);
+        ok = __all_sync(0xffffffffu, ok);
         tc_fence_after_sync();
       }
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step, ++it) {
@@ -429,9 +442,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #endif
         ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
                        kDevTimeoutTmemEmpty);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-        HY3D_TRACE_EVENT(1, tr, 6, it);
+        if (issuer) HY3D_TRACE_EVENT(1, tr, 6, it);
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.acc_cols);
         uint32_t acc = 0;   // the first MMA of a tile overwrites the accumulator
         if (b_res) {
@@ -440,65 +454,71 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           for (int kb = 0; kb < p.num_kb; ++kb) {
             ok = wait_full();
             if (!ok) break;
-            HY3D_TRACE_FINE(1, tr, 22, kb);
+            if (issuer) HY3D_TRACE_FINE(1, tr, 22, kb);
             const int ksteps = kb + 1 < p.num_kb ? 4 : p.last_ksteps;
-            if (do_mma) {
-              for (int k = 0; k < ksteps; ++k) {
-                mma_i8_lohi<kG>(d_tmem, a_lo + 2 * k, xb + 2 * k, desc_hi, idesc, acc);
-                acc = 1u;
+            if (issuer) {
+              if (do_mma) {
+                for (int k = 0; k < ksteps; ++k)
+                  mma_i8_lohi<kG>(d_tmem, a_lo + 2 * k, xb + 2 * k, desc_hi, idesc, k ? 1u : acc);
               }
+              commit_empty();
+              HY3D_TRACE_FINE(1, tr, 23, kb);
             }
-            commit_empty();
-            HY3D_TRACE_FINE(1, tr, 23, kb);
+            acc = 1u;
             next_stage();
             xb += b_atom;
           }
-          if (ok) {
+          if (ok && issuer) {
             HY3D_TRACE_EVENT(1, tr, 3, it);
             tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
           }
+          __syncwarp();
           continue;
         }
         for (int kb = 0; kb < full_kb; ++kb) {
           ok = wait_full();
           if (!ok) break;
-          if (do_mma) {
-            uint32_t xa = a_lo, xb = a_lo + b_off;
+          if (issuer) {
+            if (do_mma) {
+              uint32_t xa = a_lo, xb = a_lo + b_off;
 #pragma unroll
-            for (int a = 0; a < kAtoms; ++a) {
-              mma_i8_lohi<kG>(d_tmem, xa, xb, desc_hi, idesc, acc);
-              mma_i8_lohi<kG>(d_tmem, xa + 2, xb + 2, desc_hi, idesc, 1u);
-              mma_i8_lohi<kG>(d_tmem, xa + 4, xb + 4, desc_hi, idesc, 1u);
-              mma_i8_lohi<kG>(d_tmem, xa + 6, xb + 6, desc_hi, idesc, 1u);
-              acc = 1u;
-              xa += a_atom;
-              xb += b_atom;
+              for (int a = 0; a < kAtoms; ++a) {
+                mma_i8_lohi<kG>(d_tmem, xa, xb, desc_hi, idesc, a ? 1u : acc);
+                mma_i8_lohi<kG>(d_tmem, xa + 2, xb + 2, desc_hi, idesc, 1u);
+                mma_i8_lohi<kG>(d_tmem, xa + 4, xb + 4, desc_hi, idesc, 1u);
+                mma_i8_lohi<kG>(d_tmem, xa + 6, xb + 6, desc_hi, idesc, 1u);
+                xa += a_atom;
+                xb += b_atom;
+              }
             }
+            commit_empty();
           }
           acc = 1u;
-          commit_empty();
           next_stage();
         }
         if (ok && full_kb < p.num_kb) {   // ragged last stage: fewer K steps
           ok = wait_full();
           if (ok) {
-            if (do_mma) {
-              for (int k = 0; k < p.last_ksteps; ++k) {
-                const uint32_t at = static_cast<uint32_t>(k >> 2), kk = static_cast<uint32_t>(k & 3);
-                mma_i8_lohi<kG>(d_tmem, a_lo + at * a_atom + 2 * kk,
-                                a_lo + b_off + at * b_atom + 2 * kk, desc_hi, idesc, acc);
-                acc = 1u;
+            if (issuer) {
+              if (do_mma) {
+                for (int k = 0; k < p.last_ksteps; ++k) {
+                  const uint32_t at = static_cast<uint32_t>(k >> 2), kk = static_cast<uint32_t>(k & 3);
+                  mma_i8_lohi<kG>(d_tmem, a_lo + at * a_atom + 2 * kk,
+                                  a_lo + b_off + at * b_atom + 2 * kk, desc_hi, idesc, k ? 1u : acc);
+                }
               }
+              commit_empty();
             }
-            commit_empty();
+            acc = 1u;
             next_stage();
           }
         }
-        if (ok) {
+        if (ok && issuer) {
           HY3D_TRACE_EVENT(1, tr, 3, it);
           if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
           else tc_commit_2cta(smem_u32(&ctrl->tmem_full[buf]), 3);
         }
+        __syncwarp();
       }
     }
     __syncwarp();
