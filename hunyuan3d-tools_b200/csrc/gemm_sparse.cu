@@ -96,7 +96,10 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                                                    kEpiWarps * kSlabBytes);
   volatile int* abort_flag = &ctrl->abort_flag;
 
-  const int warp = threadIdx.x >> 5;
+  // Warp index through a shuffle: known warp-uniform to the compiler, so the producer and MMA
+  // roles run as warp-uniform loops (all lanes wait, lane 0 issues) with their descriptors and
+  // coordinates in uniform registers.
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const int total_tiles = p.w_tiles * p.t_tiles;       // w_tiles counts 128*kG-row units
   const uint32_t cta_rank = kG == 2 ? cluster_cta_rank() : 0u;
@@ -142,8 +145,9 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   pdl_wait();
 
   if (warp == 0) {
-    // ---------------- TMA producer (one thread) ----------------
-    if (lane == 0) {
+    // ---------------- TMA producer (all lanes walk the loop, lane 0 issues) ----------------
+    {
+      const bool issuer = lane == 0;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -152,11 +156,14 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const int t0 = (tile / p.w_tiles) * p.block_t + tok_off;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           const uint32_t full = smem_u32(&ctrl->full[stage]);
           const uint32_t sa = smem_base + stage * stage_bytes;
           const uint32_t sb = sa + kABytes + kEBytes;
-          if (kG == 1) {
+          if (!issuer) {
+            // only lane 0 issues
+          } else if (kG == 1) {
             mbar_arrive_expect_tx(full, stage_bytes);
             tma_load_2d(sa, &tm_w, full, kb * (kBlockK / 2), w0);
             tma_load_2d(sa + kABytes, &tm_e, full, kb * (kBlockK / 8), w0);
@@ -180,7 +187,8 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer (one thread) ----------------
-    if (lane == 0 && leader) {
+    if (leader) {
+      const bool issuer = lane == 0;
       const uint32_t idesc = make_idesc_i8(kTileW * kG, static_cast<uint32_t>(p.block_t), true);
       const uint64_t desc128 = make_smem_desc(0, 1024, 128);
       const uint64_t desc_e = make_smem_desc(0, 128, 0);
@@ -193,11 +201,13 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const uint32_t acc_phase = (it >> 1) & 1;
         ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
                        kDevTimeoutTmemEmpty);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.block_t);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          ok = mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag, kDevTimeoutFull);
+          ok = mbar_wait<true>(smem_u32(&ctrl->full[stage]), phase, abort_flag, kDevTimeoutFull);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           const uint32_t sa = smem_base + stage * stage_bytes;
           const uint32_t se = sa + kABytes;
@@ -208,6 +218,7 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           // Metadata of the stage: two 128-lane x 128-bit copies = 8 columns = four K=64 steps.
           const uint64_t de0 = desc_e | static_cast<uint64_t>((se & 0x3FFFFu) >> 4);
           const uint64_t de1 = desc_e | static_cast<uint64_t>(((se + kEBytes / 2) & 0x3FFFFu) >> 4);
+          if (issuer) {
           if (kG == 1) {
             tmem_cp_128x128b_1cta(tmem_base + e_col, de0);
             tmem_cp_128x128b_1cta(tmem_base + e_col + 4, de1);
@@ -232,12 +243,14 @@ gemm_sparse_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           }
           if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->empty[stage]));
           else tc_commit_2cta(smem_u32(&ctrl->empty[stage]), 3);
+          }   // issuer
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
-        if (ok) {
+        if (ok && issuer) {
           if (kG == 1) tc_commit_1cta(smem_u32(&ctrl->tmem_full[buf]));
           else tc_commit_2cta(smem_u32(&ctrl->tmem_full[buf]), 3);
         }
+        __syncwarp();
       }
     }
     __syncwarp();
