@@ -50,7 +50,6 @@ struct DenseArgs {
   int M, N, K;
   int block_n, stages, acc_cols, tma_store, store_bufs;
   int b_resident;  // the CTA's B tile (all K blocks) is loaded once and stays in shared memory
-  int wide;    // TMA-store path with 64-column (128-byte) slabs, one per epilogue warp and tile
   int m_tiles, n_tiles, num_kb, last_ksteps, n_fastest;
   int atoms;   // 128-byte K blocks per pipeline stage (1 or 2)
   int debug;   // knock-out switches of -DHY3D_TRACE builds (always 0 in the shipped library)
@@ -77,12 +76,6 @@ struct __align__(16) DenseCtrl {
   } while (0)
 #else
 #define HY3D_EPI_TRACE(ev, arg) ((void)0)
-#endif
-
-#ifdef HY3D_KO
-#define HY3D_KO_ARG , p.debug
-#else
-#define HY3D_KO_ARG
 #endif
 
 __device__ __forceinline__ void epi_bar_sync() {
@@ -178,60 +171,10 @@ __device__ __forceinline__ void slab_store(const uint32_t (&packed)[16], uint32_
   }
 }
 
-// 16 accumulator columns of one row -> 16 outputs packed in 8 words, written as two 16-byte
-// pieces (chunks 2k, 2k+1) of the row's 128-byte line in a wide staging buffer (128-byte
-// swizzle: 16-byte chunk c of row r sits at c ^ (r & 7)).
-template <bool kBf16, int kEpi>
-__device__ __forceinline__ void chunk_math_store_wide(const uint32_t (&r)[16], float2 as2,
-                                                      const float* wsb, const float* bsb,
-                                                      uint32_t row_addr, uint32_t sw, uint32_t k,
-                                                      int dbg = 0) {
-  uint32_t packed[8];
-#ifdef HY3D_KO
-  if (dbg & 64) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) packed[j] = r[j] ^ r[j + 8];
-  } else
-#endif
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    float4 w4, b4;
-#ifdef HY3D_KO
-    if (dbg & 8) { w4 = make_float4(as2.x, 1.f, as2.x, 2.f); b4 = make_float4(1.f, as2.x, 2.f, as2.x); } else
-#endif
-    {
-      w4 = *reinterpret_cast<const float4*>(wsb + 4 * q);
-      b4 = *reinterpret_cast<const float4*>(bsb + 4 * q);
-    }
-    const float2 s01 = __fmul2_rn(as2, make_float2(w4.x, w4.y));
-    const float2 s23 = __fmul2_rn(as2, make_float2(w4.z, w4.w));
-    const float2 a01 = make_float2(static_cast<float>(static_cast<int32_t>(r[4 * q + 0])),
-                                   static_cast<float>(static_cast<int32_t>(r[4 * q + 1])));
-    const float2 a23 = make_float2(static_cast<float>(static_cast<int32_t>(r[4 * q + 2])),
-                                   static_cast<float>(static_cast<int32_t>(r[4 * q + 3])));
-    float2 y01 = __ffma2_rn(a01, s01, make_float2(b4.x, b4.y));
-    float2 y23 = __ffma2_rn(a23, s23, make_float2(b4.z, b4.w));
-    if (kEpi == HY3D_EPI_GELU) {
-      y01.x = gelu_erf(y01.x); y01.y = gelu_erf(y01.y); y23.x = gelu_erf(y23.x); y23.y = gelu_erf(y23.y);
-    }
-    packed[2 * q] = pack2t<kBf16>(y01.x, y01.y);
-    packed[2 * q + 1] = pack2t<kBf16>(y23.x, y23.y);
-  }
-#ifdef HY3D_KO
-  if (dbg & 16) {
-    if ((packed[0] ^ packed[3] ^ packed[5] ^ packed[7]) == 0x12345678u) st_shared_v4(row_addr, 0, 0, 0, 0);
-    return;
-  }
-#endif
-  st_shared_v4(row_addr + (((2u * k) ^ sw) << 4), packed[0], packed[1], packed[2], packed[3]);
-  st_shared_v4(row_addr + (((2u * k + 1u) ^ sw) << 4), packed[4], packed[5], packed[6], packed[7]);
-}
-
 template <bool kBf16, int kEpi, int kG, int kAtoms>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                  const __grid_constant__ CUtensorMap tm_o, const __grid_constant__ CUtensorMap tm_ow,
-                  const DenseArgs p) {
+                  const __grid_constant__ CUtensorMap tm_o, const DenseArgs p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   const uint32_t smem_base = smem_u32(smem_raw);
@@ -288,7 +231,6 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
     if (p.tma_store) tma_prefetch_desc(&tm_o);
-    if (p.wide) tma_prefetch_desc(&tm_ow);
   }
   if (warp == 1) {
     if (kG == 2) {
@@ -329,9 +271,6 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const int m0 = tile_m(tile) * (kTileM * kG) + row_off;
         const int n0 = tile_n(tile) * p.block_n + col_off;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-#ifdef HY3D_KO
-          if (p.debug & 256) ok = mbar_wait<true>(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty); else
-#endif
           ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
@@ -437,9 +376,6 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-#ifdef HY3D_KO
-        if (p.debug & 512) ok = mbar_wait<true>(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag, kDevTimeoutTmemEmpty); else
-#endif
         ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
                        kDevTimeoutTmemEmpty);
         ok = __all_sync(0xffffffffu, ok);
@@ -591,9 +527,6 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         cur_n0 = n0;
       }
       const long long w0c = HY3D_CLK();
-#ifdef HY3D_KO
-      if (ok && (p.debug & 1024)) ok = mbar_wait<true>(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag, kDevTimeoutTmemFull); else
-#endif
       if (ok) ok = mbar_wait(smem_u32(&ctrl->tmem_full[buf]), acc_phase, abort_flag,
                              kDevTimeoutTmemFull);
       const long long w1c = HY3D_CLK();
@@ -614,62 +547,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #else
       constexpr bool skip_epilogue = false;
 #endif
-      if (kEpi != HY3D_EPI_GEGLU && p.wide && !skip_epilogue) {
-        // One slab per warp and tile: warp `half` of a quarter takes the 64 columns
-        // [64*half, 64*half+64) as one 128-byte-wide store, or the 32-column remainder of the
-        // tile as a narrow one.  The accumulator is read in 16-column pieces, the next piece
-        // in flight while the current one is rescaled and staged.
-        const int out_row = m0 + quarter * 32;
-        const bool rows_in = out_row < p.M;
-        const int nwide = p.block_n >> 6;
-        const int c0 = half << 6;
-        const float2 as2 = make_float2(as, as);
-        if (half < nwide) {
-          const uint32_t row_addr = stage_buf + static_cast<uint32_t>(lane) * 128u;
-          const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
-          uint32_t ra[16], rb[16];
-          __syncwarp();
-          tmem_ld_x16(t_row + c0, ra);
-          tmem_ld_wait_for(ra);
-          HY3D_EPI_TRACE(10, it);
-          tmem_ld_x16(t_row + c0 + 16, rb);
-          tma_store_wait_read<0>();   // this warp's previous store has read the buffer
-          __syncwarp();
-          HY3D_EPI_TRACE(11, it);
-          chunk_math_store_wide<kBf16, kEpi>(ra, as2, wsb + c0, bsb + c0, row_addr, sw, 0u HY3D_KO_ARG);
-          tmem_ld_wait_for(rb);
-          tmem_ld_x16(t_row + c0 + 32, ra);
-          chunk_math_store_wide<kBf16, kEpi>(rb, as2, wsb + c0 + 16, bsb + c0 + 16, row_addr, sw, 1u HY3D_KO_ARG);
-          tmem_ld_wait_for(ra);
-          tmem_ld_x16(t_row + c0 + 48, rb);
-          chunk_math_store_wide<kBf16, kEpi>(ra, as2, wsb + c0 + 32, bsb + c0 + 32, row_addr, sw, 2u HY3D_KO_ARG);
-          tmem_ld_wait_for(rb);
-          HY3D_EPI_TRACE(12, it);
-          release_acc(smem_u32(&ctrl->tmem_empty[buf]));
-          arrived = true;
-          chunk_math_store_wide<kBf16, kEpi>(rb, as2, wsb + c0 + 48, bsb + c0 + 48, row_addr, sw, 3u HY3D_KO_ARG);
-          HY3D_EPI_TRACE(13, it);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-#ifdef HY3D_KO
-            if (p.debug & 48) { /* store knocked out */ } else
-#endif
-            if (rows_in && n0 + c0 < p.N) tma_store_2d(&tm_ow, stage_buf, (n0 + c0) * 2, out_row);
-            tma_store_commit();
-          }
-        } else if (half == nwide && (p.block_n & 32)) {
-          uint32_t r[32], packed[16];
-          __syncwarp();
-          tmem_ld_x32(t_row + c0, r);
-          tmem_ld_wait();
-          release_acc(smem_u32(&ctrl->tmem_empty[buf]));
-          arrived = true;
-          slab_math<kBf16, kEpi>(r, as, wsb + c0, bsb + c0, packed);
-          slab_store(packed, stage_buf, lane, 0, &tm_o, (n0 + c0) * 2, out_row,
-                     rows_in && n0 + c0 < p.N);
-        }
-      } else if (p.tma_store && !skip_epilogue) {
+      if (p.tma_store && !skip_epilogue) {
         const int nslab = p.block_n / acc_per_slab;
         const int out_row = m0 + quarter * 32;
         const bool rows_in = out_row < p.M;
@@ -934,10 +812,11 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   const int staging1 = kEpiWarps * kSlabBytes;
   int b_resident = 0, store_bufs = 2, stages = 0, stage_bytes = 0;
   if (group == 1 && atoms == 1 && column_fixed && total_tiles >= 2 * clusters) {
-    for (int bufs = p.tma_store ? 2 : 1; bufs >= 1 && !b_resident; --bufs) {
-      const int st = (kSmemLimit - ctrl_bytes - bufs * staging1 - b_tile_bytes) / a_stage;
-      if (st >= 4) { b_resident = 1; store_bufs = bufs; stages = st; stage_bytes = a_stage; }
-    }
+    // One staging buffer per epilogue warp: measured faster than two here (a warp that must
+    // wait for its previous store to leave shared memory paces the store stream, and the
+    // loads queue behind fewer stores).
+    const int st = (kSmemLimit - ctrl_bytes - staging1 - b_tile_bytes) / a_stage;
+    if (st >= 4) { b_resident = 1; store_bufs = 1; stages = st; stage_bytes = a_stage; }
   }
 #if defined(HY3D_TRACE) || defined(HY3D_KO)
   if (const char* e = getenv("HY3D_B_RESIDENT")) { if (!atoi(e)) b_resident = 0; }
@@ -956,9 +835,6 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   }
   p.b_resident = b_resident;
   p.store_bufs = store_bufs;
-  // Wide (128-byte) store slabs need the 4 KB of two narrow buffers per warp and at least three
-  // slabs per quarter to keep three of its four warps busy; narrower tiles keep 32-column slabs.
-  p.wide = (p.tma_store && !geglu && store_bufs == 2 && block_n >= 160) ? 1 : 0;
   const int fixed = ctrl_bytes + store_bufs * staging1 + (b_resident ? b_tile_bytes : 0);
   if (stages > kMaxStages) stages = kMaxStages;
 #ifdef HY3D_TRACE
@@ -972,7 +848,7 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
 #endif
   const int smem_bytes = stages * stage_bytes + fixed;
 
-  CUtensorMap tm_a, tm_b, tm_o, tm_ow;
+  CUtensorMap tm_a, tm_b, tm_o;
   int rc = encode_tmap_2d_u8(&tm_a, A, static_cast<uint64_t>(K), static_cast<uint64_t>(M),
                              static_cast<uint64_t>(K), kBlockKBytes, kTileM, 128);
   if (rc != HY3D_OK) return rc;
@@ -988,16 +864,8 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   } else {
     tm_o = tm_a;   // unused by the kernel
   }
-  if (p.wide) {
-    const uint64_t row_bytes = static_cast<uint64_t>(N) * 2;
-    rc = encode_tmap_2d_u8(&tm_ow, out, row_bytes, static_cast<uint64_t>(M), row_bytes, 128, 32, 128);
-    if (rc != HY3D_OK) return rc;
-  } else {
-    tm_ow = tm_a;  // unused by the kernel
-  }
 
-  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                            const DenseArgs);
+  using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const DenseArgs);
   // [0]: one CTA per tile, [1]: CTA pairs, [2]: CTA pairs with deep (two-block) stages.
 #define HY3D_DENSE_ROW(G, A)                                                              \
   {{gemm_dense_kernel<false, HY3D_EPI_LINEAR, G, A>, gemm_dense_kernel<false, HY3D_EPI_GELU, G, A>, \
@@ -1026,7 +894,7 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  if (cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_o, tm_ow, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b, tm_o, p) != cudaSuccess) {
     cudaGetLastError();
     return HY3D_ERR_CUDA;
   }

@@ -60,7 +60,8 @@ int linear_dense_static(const void* x, int x_dtype, int64_t ldx, const int8_t* B
                         void* out, int out_dtype, int64_t M, int64_t N, int64_t K, int epilogue,
                         cudaStream_t stream) {
   if (M < 0 || K <= 0 || N <= 0) return HY3D_ERR_SHAPE;
-  if (M > kStaticMaxRows || M * K > kStaticQBytes) return HY3D_ERR_TOO_LARGE;
+  // K is bounded first so that the product below cannot overflow.
+  if (M > kStaticMaxRows || K > kStaticQBytes || M * K > kStaticQBytes) return HY3D_ERR_TOO_LARGE;
   unsigned char* base = nullptr;
   int rc = scratch_address(&base);
   if (rc != HY3D_OK) return rc;

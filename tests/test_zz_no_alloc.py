@@ -31,6 +31,24 @@ def test_static_scratch_matches_regular_entry_point_twice(tc):
         assert float((got.float() - expect.float()).abs().max()) == 0.0   # tolerance: none needed
 
 
+def test_static_scratch_call_leaves_device_memory_as_it_found_it(tc):
+    """After a first call (which may load the module's code and resolve the scratch address),
+    further calls change neither the caching allocator's figure nor the driver's free-memory
+    figure: the entry point allocates nothing."""
+    x, w, ws, b = _case(2048, 640, 640, 3, torch.bfloat16)
+    out = torch.empty(2048, 640, dtype=torch.bfloat16, device=DEV)
+    tc.int8_linear_tc_static(x, w, ws, b, out=out)
+    torch.cuda.synchronize()
+    allocated, reserved = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        tc.int8_linear_tc_static(x, w, ws, b, out=out)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == allocated and torch.cuda.memory_reserved() == reserved
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+
+
 def test_static_scratch_rejects_oversize(tc):
     lib = tc._lib
     max_bytes, max_rows = lib.hy3d_static_scratch_max_bytes(), lib.hy3d_static_scratch_max_rows()
