@@ -806,6 +806,23 @@ def run_one_shape(args):
     status codes.  Nothing is timed here: a profiler does that."""
     ctx = Ctx()
     lib, sp, dev = ctx.lib, ctx.sp, "cuda"
+    if args.kernel == "unet":
+        # `--launches` eager (un-graphed) forward passes of the full-size UNet of configs[3], so
+        # that a profiler's launch list shows every kernel of a denoise step by name.
+        mm = importlib.import_module(PKG + ".multimesh")
+        unet, _ = mm.build_texture_unet(dev, torch.bfloat16, args.quant, seed=0, init_on_device=True)
+        lat, cond, uncond = mm.mesh_inputs(0, device=dev)
+        x = torch.cat([lat, lat]); c = torch.cat([uncond, cond])
+        t = torch.full((12,), 500, device=dev)
+        with torch.no_grad():
+            for _ in range(args.launches):
+                unet(x, t, c)
+        torch.cuda.synchronize()
+        if ctx.tc.device_status() != 0:
+            raise SystemExit("device status non-zero")
+        print("ok")
+        ctx.close()
+        return
     M, K, N = (int(v) for v in args.shape.split("x"))
     x = torch.randn(M, K, device=dev).bfloat16()
     q = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev)
@@ -946,7 +963,7 @@ def main():
                     choices=["dense_sweep", "sparse_sweep", "unet", "multimesh", "one_shape", "ref_kernels"])
     ap.add_argument("--quant", default="mixed", choices=["mixed", "dense", "sparse", "none"])
     ap.add_argument("--quick", action="store_true", help="headline, roofline and e2e only: no sub-records")
-    ap.add_argument("--kernel", default="dense", help="one_shape: dense | sparse | quant | lnquant | prune | fused")
+    ap.add_argument("--kernel", default="dense", help="one_shape: dense | sparse | quant | lnquant | prune | fused | unet (eager UNet forwards)")
     ap.add_argument("--shape", default="8192x1280x1280", help="one_shape: MxKxN")
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--cpu-frac", type=float, default=None,

@@ -221,16 +221,21 @@ int launch_quantize(const void* x, int64_t M, int64_t K, int64_t ldx, int8_t* q,
 // G <= 32 lanes share a row (shuffle reductions); gamma / beta are staged once per block in
 // shared memory as fp32 and the block walks rows with a grid-stride loop.
 template <bool kBf16, int kMaxV>
-__global__ void __launch_bounds__(kQuantThreads)
+__global__ void __launch_bounds__(kQuantThreads, kMaxV <= 4 ? 3 : 2)
 layernorm_quantize_kernel(const uint16_t* __restrict__ x, int64_t ldx, const void* __restrict__ gamma,
                           const void* __restrict__ beta, int gb_dtype, float eps,
                           int8_t* __restrict__ q, float* __restrict__ scale_out,
                           uint16_t* __restrict__ y_out, int64_t M, int K, int G) {
-  extern __shared__ float s_gb[];            // gamma[K] then beta[K]
+  extern __shared__ float s_gb[];            // gamma and beta as fp32, 2 * K floats in planes
   pdl_launch_dependents();
+  // Four planes of K/8 float4 each: [gamma 0-3 | gamma 4-7 | beta 0-3 | beta 4-7] of every
+  // 8-element vector, so that the 16-byte loads of neighbouring lanes (neighbouring vectors)
+  // are contiguous and conflict-free.
+  const int plane = (K >> 3) * 4;
   for (int k = threadIdx.x; k < K; k += blockDim.x) {
-    s_gb[k] = gamma ? load_scalar(gamma, gb_dtype, k) : 1.0f;
-    s_gb[K + k] = beta ? load_scalar(beta, gb_dtype, k) : 0.0f;
+    const int at = ((k >> 2) & 1) * plane + (k >> 3) * 4 + (k & 3);
+    s_gb[at] = gamma ? load_scalar(gamma, gb_dtype, k) : 1.0f;
+    s_gb[2 * plane + at] = beta ? load_scalar(beta, gb_dtype, k) : 0.0f;
   }
   pdl_wait();   // x comes from the previous kernel in the stream; gamma / beta are parameters
   __syncthreads();
@@ -239,34 +244,58 @@ layernorm_quantize_kernel(const uint16_t* __restrict__ x, int64_t ldx, const voi
   const int sub = tid % G;
   const int nvec = K >> 3;
   const float inv_k = 1.0f / static_cast<float>(K);
-  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_block; row0 < M;
-       row0 += static_cast<int64_t>(gridDim.x) * rows_per_block) {
-    const int64_t row = row0 + tid / G;
-    const bool row_ok = row < M;
-    const uint4* src = reinterpret_cast<const uint4*>(x + (row_ok ? row : 0) * ldx);
-    float f[kMaxV][8];
-    float sum = 0.0f;
+  // The next row's vectors are requested before the current row is worked on, so that every
+  // warp keeps loads in flight through its reductions.
+  const int64_t row_step = static_cast<int64_t>(gridDim.x) * rows_per_block;
+  uint4 vn[kMaxV];
+  auto fetch = [&](int64_t r0) {
+    const int64_t r = r0 + tid / G;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (r < M ? r : 0) * ldx);
 #pragma unroll
     for (int i = 0; i < kMaxV; ++i) {
       const int c = sub + i * G;
-      const uint4 v = (row_ok && c < nvec) ? __ldcs(src + c) : make_uint4(0, 0, 0, 0);
-      unpack8<kBf16>(v, f[i]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) sum += f[i][j];
+      vn[i] = (r < M && c < nvec) ? __ldcs(src + c) : make_uint4(0, 0, 0, 0);
     }
+  };
+  fetch(static_cast<int64_t>(blockIdx.x) * rows_per_block);
+  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_block; row0 < M; row0 += row_step) {
+    const int64_t row = row0 + tid / G;
+    const bool row_ok = row < M;
+    // The row lives in registers as pairs; every step below is a packed fp32x2 instruction
+    // (two IEEE single-precision operations per issue slot).
+    float2 f[kMaxV][4];
+    float2 sum2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < kMaxV; ++i) {
+      float t[8];
+      unpack8<kBf16>(vn[i], t);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        f[i][j] = make_float2(t[2 * j], t[2 * j + 1]);
+        sum2 = __fadd2_rn(sum2, f[i][j]);
+      }
+    }
+    if (row0 + row_step < M) fetch(row0 + row_step);
+    float sum = sum2.x + sum2.y;
     for (int off = G >> 1; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
     const float mean = sum * inv_k;
-    float ss = 0.0f;
+    const float2 nmean2 = make_float2(-mean, -mean);
+    float2 ss2 = make_float2(0.0f, 0.0f);
 #pragma unroll
     for (int i = 0; i < kMaxV; ++i) {
       const int c = sub + i * G;
       if (c < nvec) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { const float d = f[i][j] - mean; ss = fmaf(d, d, ss); }
+        for (int j = 0; j < 4; ++j) {
+          f[i][j] = __fadd2_rn(f[i][j], nmean2);          // centred from here on
+          ss2 = __ffma2_rn(f[i][j], f[i][j], ss2);
+        }
       }
     }
+    float ss = ss2.x + ss2.y;
     for (int off = G >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
     const float rstd = __frcp_rn(__fsqrt_rn(fmaf(ss, inv_k, eps)));
+    const float2 rstd2 = make_float2(rstd, rstd);
     // normalise, round to the activation type, keep the rounded values for the quantiser
     uint32_t amax2 = 0;
     uint4 yv[kMaxV];
@@ -275,23 +304,24 @@ layernorm_quantize_kernel(const uint16_t* __restrict__ x, int64_t ldx, const voi
       const int c = sub + i * G;
       yv[i] = make_uint4(0, 0, 0, 0);
       if (c < nvec) {
-        const float4 g0 = *reinterpret_cast<const float4*>(s_gb + 8 * c);
-        const float4 g1 = *reinterpret_cast<const float4*>(s_gb + 8 * c + 4);
-        const float4 b0 = *reinterpret_cast<const float4*>(s_gb + K + 8 * c);
-        const float4 b1 = *reinterpret_cast<const float4*>(s_gb + K + 8 * c + 4);
-        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const float4 g0 = *reinterpret_cast<const float4*>(s_gb + 4 * c);
+        const float4 g1 = *reinterpret_cast<const float4*>(s_gb + plane + 4 * c);
+        const float4 b0 = *reinterpret_cast<const float4*>(s_gb + 2 * plane + 4 * c);
+        const float4 b1 = *reinterpret_cast<const float4*>(s_gb + 3 * plane + 4 * c);
+        const float2 gg[4] = {make_float2(g0.x, g0.y), make_float2(g0.z, g0.w),
+                              make_float2(g1.x, g1.y), make_float2(g1.z, g1.w)};
+        const float2 bb[4] = {make_float2(b0.x, b0.y), make_float2(b0.z, b0.w),
+                              make_float2(b1.x, b1.y), make_float2(b1.z, b1.w)};
         uint32_t w[4];
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          const float y0 = fmaf((f[i][j] - mean) * rstd, gg[j], bb[j]);
-          const float y1 = fmaf((f[i][j + 1] - mean) * rstd, gg[j + 1], bb[j + 1]);
+        for (int j = 0; j < 4; ++j) {
+          const float2 y = __ffma2_rn(__fmul2_rn(f[i][j], rstd2), gg[j], bb[j]);
           if (kBf16) {
-            const __nv_bfloat162 h = __floats2bfloat162_rn(y0, y1);
-            w[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            const __nv_bfloat162 h = __floats2bfloat162_rn(y.x, y.y);
+            w[j] = *reinterpret_cast<const uint32_t*>(&h);
           } else {
-            const __half2 h = __floats2half2_rn(y0, y1);
-            w[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            const __half2 h = __floats2half2_rn(y.x, y.y);
+            w[j] = *reinterpret_cast<const uint32_t*>(&h);
           }
         }
         yv[i] = make_uint4(w[0], w[1], w[2], w[3]);
