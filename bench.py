@@ -733,12 +733,19 @@ def unet_record(ctx: Ctx, args):
     mm = importlib.import_module(PKG + ".multimesh")
     out = {"config": "BASELINE configs[3]: SD2.1-architecture UNet, 2 (CFG) x 6 views x 64x64x4 latents, "
                      "multiview attention, random init", "unit": "ms/step", "steps": 20}
-    for quant in ("dense", "mixed", "none"):
-        unet, stats = mm.build_texture_unet(ctx.dev, torch.bfloat16, quant, seed=0, init_on_device=True)
+    # "none": the stock PyTorch model (bf16 linears, torch GroupNorm); "none_nhwc_groupnorm": the
+    # same with this library's channels-last GroupNorm kernel, so that the INT8 linears' own
+    # contribution can be read off as (none_nhwc_groupnorm - dense); "mixed_torch_groupnorm":
+    # the INT8 model with torch's GroupNorm.
+    variants = (("dense", "dense", None), ("mixed", "mixed", None), ("none", "none", False),
+                ("none_nhwc_groupnorm", "none", True), ("mixed_torch_groupnorm", "mixed", False))
+    for key, quant, fused_gn in variants:
+        unet, stats = mm.build_texture_unet(ctx.dev, torch.bfloat16, quant, seed=0, init_on_device=True,
+                                            fused_gn=fused_gn)
         step = mm.GraphedStep(unet, 12, 64, 77, 1024, torch.bfloat16, ctx.dev)
         runs = timed_repeats(ctx, step.graph.replay, 20, 3, repeats=3)
-        out[quant] = round(statistics.median(runs), 3)
-        if quant == "mixed":
+        out[key] = round(statistics.median(runs), 3)
+        if key == "mixed":
             out["mixed_layers"] = {k: v for k, v in stats.items() if isinstance(v, int)}
             ctx._unet_mixed = unet        # reused by the multi-mesh record
         else:

@@ -62,6 +62,8 @@ SIGNATURES = {
     "hy3d_probe_mma_i8": [c_int, c_int, c_int, c_void_p, c_void_p],
     "hy3d_probe_hbm": [c_int, c_void_p, c_void_p, c_int64, c_void_p],
     "hy3d_probe_tmem_ld": [c_int, c_int, c_int, c_void_p, c_void_p],
+    "hy3d_groupnorm_nhwc": [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int,
+                            ctypes.c_float, c_int, c_void_p, c_void_p, c_void_p],
     "hy3d_version": [],
 }
 
@@ -85,6 +87,8 @@ def configure(lib: ctypes.CDLL) -> ctypes.CDLL:
     for name in ("hy3d_static_scratch_max_bytes", "hy3d_static_scratch_max_rows"):
         getattr(lib, name).restype = c_int64
         getattr(lib, name).argtypes = []
+    lib.hy3d_groupnorm_workspace_floats.restype = c_int64
+    lib.hy3d_groupnorm_workspace_floats.argtypes = [c_int64, c_int64, c_int]
     lib.hy3d_arch.restype = ctypes.c_char_p
     lib.hy3d_arch.argtypes = []
     lib.hy3d_source_digest.restype = ctypes.c_char_p
@@ -182,6 +186,31 @@ class _Base:
                 q.data_ptr(), s.data_ptr(), y.data_ptr() if y is not None else None, self._stream(x)),
                 "hy3d_layernorm_quantize")
         return (q, s, y) if return_normalised else (q, s)
+
+    def groupnorm_nhwc(self, x, groups, gamma, beta, eps, silu=False, out=None, workspace=None):
+        """GroupNorm (+ SiLU) of a channels_last (B, C, H, W) f16/bf16 tensor; the result has
+        the same shape and memory format.  ``workspace``: optional fp32 tensor of at least
+        ``groupnorm_workspace_floats(B, H*W, groups)`` elements (allocated when absent)."""
+        if x.dim() != 4 or x.dtype not in (torch.float16, torch.bfloat16) or not x.is_cuda:
+            raise RuntimeError("groupnorm_nhwc: x must be a 4-D f16/bf16 CUDA tensor")
+        if not x.is_contiguous(memory_format=torch.channels_last):
+            raise RuntimeError("groupnorm_nhwc: x must be in channels_last memory format")
+        B, C, H, W = x.shape
+        y = out if out is not None else torch.empty_like(x, memory_format=torch.channels_last)
+        need = self._lib.hy3d_groupnorm_workspace_floats(B, H * W, groups)
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(max(need, 1), dtype=torch.float32, device=x.device)
+        if gamma is not None and beta is not None and gamma.dtype != beta.dtype:
+            beta = beta.to(gamma.dtype)
+        gb = gamma if gamma is not None else beta
+        code = _DTYPE_CODE[gb.dtype] if gb is not None else F32
+        with torch.cuda.device(x.device):
+            self._check(self._lib.hy3d_groupnorm_nhwc(
+                x.data_ptr(), _DTYPE_CODE[x.dtype], B, H * W, C, groups,
+                gamma.data_ptr() if gamma is not None else None,
+                beta.data_ptr() if beta is not None else None, code, float(eps), 1 if silu else 0,
+                y.data_ptr(), workspace.data_ptr(), self._stream(x)), "hy3d_groupnorm_nhwc")
+        return y
 
     def quantizer_enum_check(self, dtype):
         """(pairs checked, codes differing from rint(x / scale)) over every 16-bit (amax, x)."""

@@ -31,7 +31,7 @@ LIB_PATH = os.path.join(_CSRC, LIB_NAME)
 # hy3d_int8.cu is the only translation unit; it #includes the kernel files listed in HEADERS.
 SOURCES = ["hy3d_int8.cu"]
 HEADERS = ["common.cuh", "quantize.cu", "prune_pack.cu", "gemm_dense.cu", "gemm_sparse.cu",
-           "linear_fused.cu", "capi.cu", "static_scratch.cu", "probes.cu", os.path.join(_REPO_INCLUDE, "hy3d_int8.h")]
+           "linear_fused.cu", "groupnorm.cu", "capi.cu", "static_scratch.cu", "probes.cu", os.path.join(_REPO_INCLUDE, "hy3d_int8.h")]
 
 _lock = threading.Lock()
 _lib = None

@@ -5,6 +5,7 @@
 #include "gemm_dense.cu"
 #include "gemm_sparse.cu"
 #include "linear_fused.cu"
+#include "groupnorm.cu"
 #include "capi.cu"
 #include "static_scratch.cu"
 #include "probes.cu"

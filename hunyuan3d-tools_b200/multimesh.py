@@ -159,14 +159,17 @@ class GraphedDenoiser:
 
 def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed: int = 0, fuse_geglu=True,
                        fuse_qkv=True, channels_last=True, verbose=False, init_on_device=False,
-                       sparse_min_k=None, fuse_ln=True, **unet_kwargs):
+                       sparse_min_k=None, fuse_ln=True, fused_gn=None, **unet_kwargs):
     """Random-init UNet of the paint configuration with its Linears swapped for INT8 layers.
     ``quant``: "mixed" (2:4 sparse where that kernel is the faster one -- or where
     K >= ``sparse_min_k`` if given -- dense elsewhere), "dense", "sparse" (the
     reference's sparse mode: small-K layers stay bf16) or "none".  ``fuse_qkv`` stacks the
     q/k/v (self-attention) and k/v (cross-attention) projections that share an input.
     ``init_on_device`` draws the random weights on the GPU instead of the CPU.  ``fuse_ln`` lets
-    the transformer blocks' LayerNorms emit int8 codes for the projections that follow them."""
+    the transformer blocks' LayerNorms emit int8 codes for the projections that follow them.
+    ``fused_gn`` runs GroupNorm (+ SiLU) through the library's channels-last kernel (default: on
+    for the INT8 modes on a CUDA device with channels_last activations, off for "none", which
+    stands for the stock PyTorch model)."""
     from . import quantize_utils as qu
     from .unet import UNetSD21MV, fuse_geglu_layers, fuse_qkv_layers, fuse_layernorm_quant
     torch.manual_seed(seed)
@@ -180,6 +183,10 @@ def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed:
         unet = UNetSD21MV(**unet_kwargs).to(dtype).to(device).eval()
     if channels_last:
         unet.use_channels_last()
+    if fused_gn is None:
+        fused_gn = quant != "none"
+    if fused_gn and channels_last and torch.device(device).type == "cuda":
+        unet.use_fused_groupnorm()
     stats = {}
     if quant == "mixed":
         stats = qu.quantize_model_mixed(unet, sparse_min_k=sparse_min_k, verbose=verbose)
@@ -195,6 +202,7 @@ def build_texture_unet(device, dtype=torch.bfloat16, quant: str = "mixed", seed:
         stats["qkv_layers_removed"] = fuse_qkv_layers(unet)
     if fuse_ln and quant in ("mixed", "dense"):
         stats["layernorms_emitting_int8"] = fuse_layernorm_quant(unet)
+    stats["groupnorms_nhwc_kernel"] = sum(1 for m in unet.modules() if getattr(m, "fused", False) is True)
     return unet, stats
 
 

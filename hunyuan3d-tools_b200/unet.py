@@ -32,20 +32,48 @@ def timestep_embedding(t: torch.Tensor, dim: int) -> torch.Tensor:
     return torch.cat([torch.cos(args), torch.sin(args)], dim=-1)
 
 
+class GroupNormNHWC(nn.GroupNorm):
+    """``nn.GroupNorm`` (optionally followed by SiLU) that, once ``fused`` is set, runs the
+    library's channels-last kernel on channels_last CUDA f16/bf16 inputs: torch's own kernel
+    takes NCHW only, so a model whose convolutions run NHWC pays two layout copies around every
+    normalisation (14 % of a denoise step, measured).  Parameters and state-dict keys are those
+    of ``nn.GroupNorm``; everywhere else (CPU, NCHW, fp32) the torch ops run."""
+
+    def __init__(self, num_groups: int, num_channels: int, eps: float = 1e-5, silu: bool = False):
+        super().__init__(num_groups, num_channels, eps=eps)
+        self.silu = silu
+        self.fused = False
+        self._ik = None
+        self._ws = None
+
+    def forward(self, x):
+        if (self.fused and x.is_cuda and x.dim() == 4 and x.dtype in (torch.float16, torch.bfloat16)
+                and x.is_contiguous(memory_format=torch.channels_last)):
+            if self._ik is None:
+                from .csrc.build import load_int8_kernels
+                self._ik = load_int8_kernels()
+            if self._ws is None or self._ws.device != x.device:
+                self._ws = torch.empty(1 << 16, dtype=torch.float32, device=x.device)
+            return self._ik.groupnorm_nhwc(x, self.num_groups, self.weight, self.bias, self.eps,
+                                           silu=self.silu, workspace=self._ws)
+        y = super().forward(x)
+        return F.silu(y) if self.silu else y
+
+
 class ResnetBlock(nn.Module):
     def __init__(self, cin: int, cout: int, temb_dim: int):
         super().__init__()
-        self.norm1 = nn.GroupNorm(32, cin, eps=1e-5)
+        self.norm1 = GroupNormNHWC(32, cin, eps=1e-5, silu=True)
         self.conv1 = nn.Conv2d(cin, cout, 3, padding=1)
         self.time_emb_proj = nn.Linear(temb_dim, cout)
-        self.norm2 = nn.GroupNorm(32, cout, eps=1e-5)
+        self.norm2 = GroupNormNHWC(32, cout, eps=1e-5, silu=True)
         self.conv2 = nn.Conv2d(cout, cout, 3, padding=1)
         self.conv_shortcut = nn.Conv2d(cin, cout, 1) if cin != cout else None
 
     def forward(self, x, temb):
-        h = self.conv1(F.silu(self.norm1(x)))
+        h = self.conv1(self.norm1(x))              # GroupNorm + SiLU
         h = h + self.time_emb_proj(F.silu(temb))[:, :, None, None]
-        h = self.conv2(F.silu(self.norm2(h)))
+        h = self.conv2(self.norm2(h))
         if self.conv_shortcut is not None:
             x = self.conv_shortcut(x)
         return x + h
@@ -130,7 +158,7 @@ class TransformerBlock(nn.Module):
 class SpatialTransformer(nn.Module):
     def __init__(self, dim: int, heads: int, context_dim: int, num_views: int):
         super().__init__()
-        self.norm = nn.GroupNorm(32, dim, eps=1e-6)
+        self.norm = GroupNormNHWC(32, dim, eps=1e-6)
         self.proj_in = nn.Linear(dim, dim)
         self.block = TransformerBlock(dim, heads, context_dim, num_views)
         self.proj_out = nn.Linear(dim, dim)
@@ -208,7 +236,7 @@ class UNetSD21MV(nn.Module):
                 self.up.append(layer)
                 cin = cout
 
-        self.norm_out = nn.GroupNorm(32, ch[0], eps=1e-5)
+        self.norm_out = GroupNormNHWC(32, ch[0], eps=1e-5, silu=True)
         self.conv_out = nn.Conv2d(ch[0], out_channels, 3, padding=1)
         # NHWC activations: the convolutions run without layout conversions and the token
         # view (B, H*W, C) the transformer blocks take is free.  Set by use_channels_last().
@@ -217,6 +245,14 @@ class UNetSD21MV(nn.Module):
     def use_channels_last(self) -> "UNetSD21MV":
         self.to(memory_format=torch.channels_last)
         self.channels_last = True
+        return self
+
+    def use_fused_groupnorm(self, on: bool = True) -> "UNetSD21MV":
+        """GroupNorm (+ SiLU) through the library's channels-last kernel (CUDA, f16/bf16,
+        channels_last activations); elsewhere the torch ops keep running."""
+        for m in self.modules():
+            if isinstance(m, GroupNormNHWC):
+                m.fused = on
         return self
 
     def forward(self, x, t, context):
@@ -243,7 +279,7 @@ class UNetSD21MV(nn.Module):
                 h = layer["attn"](h, context)
             if "up" in layer:
                 h = layer["up"](h)
-        return self.conv_out(F.silu(self.norm_out(h))).contiguous()
+        return self.conv_out(self.norm_out(h)).contiguous()
 
 
 def fuse_geglu_layers(model: nn.Module) -> int:

@@ -95,6 +95,25 @@ int hy3d_layernorm_quantize(const void* x, int x_dtype, int64_t M, int64_t K, in
                             int8_t* q, float* scale, void* y_out, void* stream);
 
 /*
+ * GroupNorm (+ optional SiLU) over channels-last activations: x and y are (B, HW, C) arrays of
+ * x_dtype (f16/bf16) with C contiguous -- the memory of a torch channels_last (B, C, H, W)
+ * tensor -- groups are runs of C / groups adjacent channels, statistics are taken over
+ * HW x C / groups elements per (sample, group) in fp32 (sum and sum of squares, fixed summation
+ * order).  y = x * (rstd * gamma[c]) + (beta[c] - mean * rstd * gamma[c]) rounded to x_dtype;
+ * with silu != 0 the rounded value v becomes v / (1 + exp(-v)), rounded again.  gamma / beta:
+ * (C) of gb_dtype or NULL.  workspace: hy3d_groupnorm_workspace_floats(B, HW, groups) floats of
+ * device memory owned by the caller (per-chunk partial sums; no initialisation needed).
+ * Requires C % 8 == 0, C % groups == 0, C <= 2560, 16-byte aligned x and y.  y may equal x.
+ * Replaces nothing in the reference (its UNet normalises with stock PyTorch); it serves the
+ * model around the INT8 layers, whose convolutions run NHWC while torch's GroupNorm kernel
+ * takes NCHW only and so costs two layout copies per call.
+ */
+int hy3d_groupnorm_nhwc(const void* x, int x_dtype, int64_t B, int64_t HW, int64_t C, int groups,
+                        const void* gamma, const void* beta, int gb_dtype, float eps, int silu,
+                        void* y, float* workspace, void* stream);
+int64_t hy3d_groupnorm_workspace_floats(int64_t B, int64_t HW, int groups);
+
+/*
  * Self-check of the quantiser's rounding (test hook, no reference counterpart).  The kernel
  * above never divides; this call enumerates on the device every pair of 16-bit patterns
  * (amax, x) of x_dtype with |x| <= amax -- every input the quantiser can meet -- and counts the

@@ -395,3 +395,47 @@ def test_layernorm_quantize_without_affine_and_argument_checks(ik):
     assert O.rel_l2(y, ref) < 3e-3
     with pytest.raises(RuntimeError):
         ik.layernorm_quantize(torch.randn(8, 4096).bfloat16().to(DEV), None, None, 1e-5)   # K > 2048
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("silu", [False, True])
+@pytest.mark.parametrize("shape", [(2, 320, 32, 32), (3, 640, 16, 16), (2, 960, 16, 16), (1, 1280, 8, 8),
+                                   (2, 2560, 8, 8), (1, 64, 5, 7), (12, 320, 64, 64)])
+def test_groupnorm_nhwc_matches_torch_fp32(ik, dtype, silu, shape):
+    """The channels-last GroupNorm (+ SiLU) kernel against torch's ops on the same values:
+    fp32 group_norm, rounded to the activation type, then (optionally) fp32 SiLU of the rounded
+    value, rounded again -- the two-op sequence the kernel replaces.  Floating point: the
+    statistics are summed in another order, so outputs may differ in the last place of the
+    16-bit type (tolerance: 3e-3 / 4e-4 relative L2 for bf16 / fp16, and no element off by more
+    than two units in the last place of the largest output)."""
+    B, C, H, W = shape
+    g = torch.Generator().manual_seed(C + H)
+    x = (torch.randn(B, C, H, W, generator=g) * 2 + 0.7).to(dtype).to(DEV).contiguous(memory_format=torch.channels_last)
+    gamma = (1 + 0.2 * torch.randn(C, generator=g)).to(dtype).to(DEV)
+    beta = (0.2 * torch.randn(C, generator=g)).to(dtype).to(DEV)
+    y = ik.groupnorm_nhwc(x, 32, gamma, beta, 1e-5, silu=silu)
+    assert y.shape == x.shape and y.is_contiguous(memory_format=torch.channels_last)
+    ref = torch.nn.functional.group_norm(x.float(), 32, gamma.float(), beta.float(), 1e-5).to(dtype)
+    if silu:
+        ref = torch.nn.functional.silu(ref.float()).to(dtype)
+    assert not torch.isnan(y).any()
+    assert O.rel_l2(y, ref) < (3e-3 if dtype == torch.bfloat16 else 4e-4)
+    ulp = (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10) * float(ref.float().abs().max())
+    assert float((y.float() - ref.float()).abs().max()) <= 2 * ulp
+    # in place
+    x2 = x.clone(memory_format=torch.channels_last)
+    ik.groupnorm_nhwc(x2, 32, gamma, beta, 1e-5, silu=silu, out=x2)
+    assert torch.equal(x2, y)
+
+
+def test_groupnorm_nhwc_argument_checks(ik):
+    x = torch.randn(2, 64, 4, 4, device=DEV).bfloat16()
+    with pytest.raises(RuntimeError):
+        ik.groupnorm_nhwc(x, 32, None, None, 1e-5)                       # NCHW memory
+    xl = x.contiguous(memory_format=torch.channels_last)
+    y = ik.groupnorm_nhwc(xl, 32, None, None, 1e-5)                      # no affine
+    ref = torch.nn.functional.group_norm(xl.float(), 32, None, None, 1e-5)
+    assert O.rel_l2(y, ref) < 3e-3
+    with pytest.raises(RuntimeError):
+        ik.groupnorm_nhwc(torch.randn(1, 60, 4, 4, device=DEV).bfloat16().contiguous(memory_format=torch.channels_last),
+                          32, None, None, 1e-5)                          # C % 8, C % groups

@@ -155,3 +155,37 @@ def test_layernorms_that_emit_int8_keep_the_model_output():
     assert not torch.isnan(yb).any()
     err = O.rel_l2(yb, ya)
     assert err < 2e-2, err          # the gate the configuration states for the model's output
+
+
+def test_nhwc_groupnorm_kernel_keeps_the_model_output():
+    """The UNet with its GroupNorms (+ SiLU) on the library's channels-last kernel against the
+    same bf16 model on torch's GroupNorm and SiLU ops, both measured against the fp32 model with
+    the same weights: the kernel sums its statistics in another order, which moves last-place
+    roundings that the random-init network amplifies, so the two bf16 models differ by about as
+    much as either differs from fp32.  Gate: the kernel's model is no further from fp32 than
+    1.25 x the torch-op model's distance, and the two bf16 models agree within 3e-2."""
+    mm = importlib.import_module(PKG_NAME + ".multimesh")
+    un = importlib.import_module(PKG_NAME + ".unet")
+    small = {k: v for k, v in SMALL.items() if k != "sparse_min_k"}
+    a, sa = mm.build_texture_unet(DEV, torch.bfloat16, "none", seed=4, fused_gn=False, **small)
+    b, sb = mm.build_texture_unet(DEV, torch.bfloat16, "none", seed=4, fused_gn=True, **small)
+    c, _ = mm.build_texture_unet(DEV, torch.float32, "none", seed=4, fused_gn=False, **small)
+    n_gn = sum(1 for m in b.modules() if isinstance(m, un.GroupNormNHWC))
+    assert sa["groupnorms_nhwc_kernel"] == 0 and sb["groupnorms_nhwc_kernel"] == n_gn > 0
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(4, 4, 16, 16, generator=g).to(DEV)
+    ctx = torch.randn(4, 7, 128, generator=g).to(DEV)
+    t = torch.full((4,), 300, device=DEV)
+    with torch.no_grad():
+        ya, yb = a(x.bfloat16(), t, ctx.bfloat16()), b(x.bfloat16(), t, ctx.bfloat16())
+        yc = c(x.bfloat16().float(), t, ctx.bfloat16().float())
+    assert not torch.isnan(yb).any()
+    ea, eb, eab = O.rel_l2(ya, yc), O.rel_l2(yb, yc), O.rel_l2(yb, ya)
+    assert eb <= 1.25 * ea + 1e-3, (ea, eb)
+    assert eab < 3e-2, eab
+    # and the INT8 model runs on the kernel too
+    m, sm = mm.build_texture_unet(DEV, torch.bfloat16, "mixed", seed=4, **SMALL)
+    assert sm["groupnorms_nhwc_kernel"] == n_gn
+    with torch.no_grad():
+        ym = m(x.bfloat16(), t, ctx.bfloat16())
+    assert not torch.isnan(ym).any()

@@ -30,7 +30,7 @@ def test_binding_table_covers_header(build_mod):
     declared = set(_declared_symbols())
     bound = set(binding.SIGNATURES) | {"hy3d_arch", "hy3d_status_string",
                                        "hy3d_static_scratch_max_bytes", "hy3d_static_scratch_max_rows",
-                                       "hy3d_source_digest"}
+                                       "hy3d_source_digest", "hy3d_groupnorm_workspace_floats"}
     assert declared == bound
 
 
