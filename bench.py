@@ -831,6 +831,21 @@ def run_one_shape(args):
         ctx.close()
         return
     M, K, N = (int(v) for v in args.shape.split("x"))
+    if args.kernel == "groupnorm":
+        # --shape is B x (H*W) x C here: GroupNorm + SiLU over a channels-last activation
+        B, HW, C = M, K, N
+        side = int(round(HW ** 0.5))
+        xg = torch.randn(B, C, side, HW // side, device=dev).bfloat16().contiguous(memory_format=torch.channels_last)
+        gam, bet = torch.randn(C, device=dev).bfloat16(), torch.randn(C, device=dev).bfloat16()
+        ik = importlib.import_module(PKG + ".csrc.build").load_int8_kernels()
+        ws = torch.empty(1 << 16, dtype=torch.float32, device=dev)
+        yg = torch.empty_like(xg, memory_format=torch.channels_last)
+        for _ in range(args.launches):
+            ik.groupnorm_nhwc(xg, 32, gam, bet, 1e-5, silu=True, out=yg, workspace=ws)
+        torch.cuda.synchronize()
+        print("ok")
+        ctx.close()
+        return
     x = torch.randn(M, K, device=dev).bfloat16()
     q = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev)
     s = torch.rand(M, device=dev) * 0.01
@@ -970,7 +985,7 @@ def main():
                     choices=["dense_sweep", "sparse_sweep", "unet", "multimesh", "one_shape", "ref_kernels"])
     ap.add_argument("--quant", default="mixed", choices=["mixed", "dense", "sparse", "none"])
     ap.add_argument("--quick", action="store_true", help="headline, roofline and e2e only: no sub-records")
-    ap.add_argument("--kernel", default="dense", help="one_shape: dense | sparse | quant | lnquant | prune | fused | unet (eager UNet forwards)")
+    ap.add_argument("--kernel", default="dense", help="one_shape: dense | sparse | quant | lnquant | prune | fused | groupnorm (shape = B x HW x C) | unet (eager UNet forwards)")
     ap.add_argument("--shape", default="8192x1280x1280", help="one_shape: MxKxN")
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--cpu-frac", type=float, default=None,

@@ -18,6 +18,7 @@
 #include "common.cuh"
 
 namespace hy3d {
+int device_sm_count();
 namespace gnorm {
 namespace {
 
@@ -47,7 +48,7 @@ template <bool kBf16>
 __global__ void __launch_bounds__(kMaxThreads)
 groupnorm_stats_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int groups,
                        int rows_per_chunk, float* __restrict__ partial) {
-  extern __shared__ float s_acc[];          // [2][C] per-channel sums, then reused per group
+  extern __shared__ float s_acc[];          // [k][2][C]: per row lane, per-channel sum / sum of squares
   pdl_launch_dependents();
   const int vec_cols = C >> 3;
   const int k = blockDim.x / vec_cols;
@@ -55,45 +56,42 @@ groupnorm_stats_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
   const int chunk = blockIdx.x, b = blockIdx.y, chunks = gridDim.x;
   const int64_t r0 = static_cast<int64_t>(chunk) * rows_per_chunk;
   const int64_t r1 = r0 + rows_per_chunk < HW ? r0 + rows_per_chunk : HW;
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) s_acc[c] = 0.0f;
   pdl_wait();
-  __syncthreads();
   float s[8], q[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) { s[j] = 0.0f; q[j] = 0.0f; }
   const uint4* base = reinterpret_cast<const uint4*>(x + (static_cast<int64_t>(b) * HW) * C) + tx;
   int64_t r = r0 + ty;
-  // two rows in flight per thread
-  for (; r + k < r1; r += 2 * k) {
-    const uint4 v0 = __ldg(base + r * vec_cols);
-    const uint4 v1 = __ldg(base + (r + k) * vec_cols);
-    float f0[8], f1[8];
-    unpack8f<kBf16>(v0, f0);
-    unpack8f<kBf16>(v1, f1);
+  // four rows in flight per thread
+  for (; r + 3 * k < r1; r += 4 * k) {
+    uint4 v[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      s[j] += f0[j] + f1[j];
-      q[j] = fmaf(f0[j], f0[j], q[j]);
-      q[j] = fmaf(f1[j], f1[j], q[j]);
+    for (int u = 0; u < 4; ++u) v[u] = __ldg(base + (r + u * k) * vec_cols);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float f[8];
+      unpack8f<kBf16>(v[u], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s[j] += f[j]; q[j] = fmaf(f[j], f[j], q[j]); }
     }
   }
   for (; r < r1; r += k) {
-    float f0[8];
-    unpack8f<kBf16>(__ldg(base + r * vec_cols), f0);
+    float f[8];
+    unpack8f<kBf16>(__ldg(base + r * vec_cols), f);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { s[j] += f0[j]; q[j] = fmaf(f0[j], f0[j], q[j]); }
+    for (int j = 0; j < 8; ++j) { s[j] += f[j]; q[j] = fmaf(f[j], f[j], q[j]); }
   }
-  // Row lanes fold into per-channel sums one lane at a time (fixed order).
-  for (int lane = 0; lane < k; ++lane) {
-    if (ty == lane) {
+  // Every row lane parks its sums in its own slice; channel c then adds the k slices in order.
+  float* mine = s_acc + static_cast<size_t>(ty) * 2 * C;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        s_acc[8 * tx + j] += s[j];
-        s_acc[C + 8 * tx + j] += q[j];
-      }
-    }
-    __syncthreads();
+  for (int j = 0; j < 8; ++j) { mine[8 * tx + j] = s[j]; mine[C + 8 * tx + j] = q[j]; }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) {
+    float a = s_acc[c];
+    for (int lane = 1; lane < k; ++lane) a += s_acc[static_cast<size_t>(lane) * 2 * C + c];
+    s_acc[c] = a;
   }
+  __syncthreads();
   const int cpg = C / groups;
   float* out = partial + ((static_cast<int64_t>(b) * chunks + chunk) * groups) * 2;
   for (int g = threadIdx.x; g < groups; g += blockDim.x) {
@@ -110,7 +108,7 @@ groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
                        int rows_per_chunk, int stat_chunks, const float* __restrict__ partial,
                        const void* __restrict__ gamma, const void* __restrict__ beta, int gb_dtype,
                        float eps, int silu, uint16_t* __restrict__ y) {
-  extern __shared__ float s_ab[];           // [C] scale then [C] shift
+  extern __shared__ float s_ab[];           // [C] scale, [C] shift, then the partial-sum scratch
   pdl_launch_dependents();
   const int vec_cols = C >> 3;
   const int k = blockDim.x / vec_cols;
@@ -119,11 +117,29 @@ groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
   const int cpg = C / groups;
   pdl_wait();
   const float inv_n = 1.0f / (static_cast<float>(HW) * static_cast<float>(cpg));
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    const int g = c / cpg;
+  // Partials -> per-group totals: `parts` threads share a group's chunks (a few independent
+  // loads each instead of one thread walking all of them), then fold in fixed order.
+  float* s_red = s_ab + 2 * C;               // [parts][groups][2]
+  const int parts = static_cast<int>(blockDim.x) / groups > 0 ? static_cast<int>(blockDim.x) / groups : 1;
+  for (int idx = threadIdx.x; idx < parts * groups; idx += blockDim.x) {
+    const int g = idx % groups, part = idx / groups;
     const float* p = partial + (static_cast<int64_t>(b) * stat_chunks * groups + g) * 2;
     float a = 0.0f, q = 0.0f;
-    for (int ch = 0; ch < stat_chunks; ++ch) { a += p[0]; q += p[1]; p += 2 * groups; }
+    for (int ch = part; ch < stat_chunks; ch += parts) {
+      a += p[static_cast<int64_t>(ch) * 2 * groups];
+      q += p[static_cast<int64_t>(ch) * 2 * groups + 1];
+    }
+    s_red[2 * idx] = a;
+    s_red[2 * idx + 1] = q;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const int g = c / cpg;
+    float a = 0.0f, q = 0.0f;
+    for (int part = 0; part < parts; ++part) {
+      a += s_red[2 * (part * groups + g)];
+      q += s_red[2 * (part * groups + g) + 1];
+    }
     const float mean = a * inv_n;
     const float var = fmaxf(fmaf(-mean, mean, q * inv_n), 0.0f);
     const float rstd = rsqrtf(var + eps);
@@ -141,9 +157,9 @@ groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
   const int64_t sample = (static_cast<int64_t>(b) * HW) * C;
   const uint4* src = reinterpret_cast<const uint4*>(x + sample) + tx;
   uint4* dst = reinterpret_cast<uint4*>(y + sample) + tx;
-  for (int64_t r = r0 + ty; r < r1; r += k) {
+  auto transform = [&](const uint4& v) {
     float f[8];
-    unpack8f<kBf16>(__ldg(src + r * vec_cols), f);
+    unpack8f<kBf16>(v, f);
     uint32_t w[4];
 #pragma unroll
     for (int j = 0; j < 8; j += 2) {
@@ -157,14 +173,24 @@ groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
           const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&packed));
           y0 = t.x; y1 = t.y;
         }
-        y0 = y0 / (1.0f + expf(-y0));
-        y1 = y1 / (1.0f + expf(-y1));
+        // fast exp / divide: their error is far below half a unit of the 16-bit result
+        y0 = __fdividef(y0, 1.0f + __expf(-y0));
+        y1 = __fdividef(y1, 1.0f + __expf(-y1));
         packed = pack2(y0, y1, kBf16 ? HY3D_BF16 : HY3D_F16);
       }
       w[j >> 1] = packed;
     }
-    dst[r * vec_cols] = make_uint4(w[0], w[1], w[2], w[3]);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  };
+  int64_t r = r0 + ty;
+  for (; r + 3 * k < r1; r += 4 * k) {          // four rows in flight per thread
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldg(src + (r + u * k) * vec_cols);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) dst[(r + u * k) * vec_cols] = transform(v[u]);
   }
+  for (; r < r1; r += k) dst[r * vec_cols] = transform(__ldg(src + r * vec_cols));
 }
 
 }  // namespace
@@ -172,7 +198,10 @@ groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
 // Rows per chunk so that B * chunks blocks fill the GPU a few times over; the statistics pass
 // and the apply pass may use different chunkings (the apply pass is told the statistics' count).
 int chunks_for(int64_t B, int64_t HW) {
-  int64_t want = (148 * 4 + B - 1) / B;             // blocks per sample
+  // One full wave: four 320-thread blocks are resident per SM (48 registers per thread), and a
+  // grid that spills a few blocks into a second wave takes twice as long.
+  const int sms = device_sm_count() > 0 ? device_sm_count() : 148;
+  int64_t want = (static_cast<int64_t>(sms) * 4) / B;   // blocks per sample, rounded down
   if (want < 1) want = 1;
   if (want > 64) want = 64;
   int64_t rows = (HW + want - 1) / want;
@@ -200,7 +229,9 @@ int groupnorm_nhwc(const void* x, int x_dtype, int64_t B, int64_t HW, int64_t C,
   const int threads = vec_cols * k;
   const int chunks = chunks_for(B, HW);
   const int rows_per_chunk = static_cast<int>((HW + chunks - 1) / chunks);
-  const size_t smem = static_cast<size_t>(2 * Ci) * sizeof(float);
+  const int parts = threads / groups > 0 ? threads / groups : 1;
+  const size_t smem = (static_cast<size_t>(2 * Ci) + static_cast<size_t>(parts) * groups * 2) * sizeof(float);  // apply
+  const size_t smem_stats = static_cast<size_t>(k) * 2 * Ci * sizeof(float);  // stats: one slice per row lane
   const bool bf16 = x_dtype == HY3D_BF16;
   const uint16_t* xp = static_cast<const uint16_t*>(x);
   uint16_t* yp = static_cast<uint16_t*>(y);
@@ -214,10 +245,12 @@ int groupnorm_nhwc(const void* x, int x_dtype, int64_t B, int64_t HW, int64_t C,
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t err;
+  cfg.dynamicSmemBytes = smem_stats;
   if (bf16) err = cudaLaunchKernelEx(&cfg, groupnorm_stats_kernel<true>, xp, HW, Ci, groups, rows_per_chunk, workspace);
   else err = cudaLaunchKernelEx(&cfg, groupnorm_stats_kernel<false>, xp, HW, Ci, groups, rows_per_chunk, workspace);
   if (err != cudaSuccess) { cudaGetLastError(); return HY3D_ERR_CUDA; }
   const float* ws = workspace;
+  cfg.dynamicSmemBytes = smem;
   if (bf16) err = cudaLaunchKernelEx(&cfg, groupnorm_apply_kernel<true>, xp, HW, Ci, groups, rows_per_chunk, chunks, ws, gamma, beta, gb_dtype, eps, silu, yp);
   else err = cudaLaunchKernelEx(&cfg, groupnorm_apply_kernel<false>, xp, HW, Ci, groups, rows_per_chunk, chunks, ws, gamma, beta, gb_dtype, eps, silu, yp);
   if (err != cudaSuccess) { cudaGetLastError(); return HY3D_ERR_CUDA; }
