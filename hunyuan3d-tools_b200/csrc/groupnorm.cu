@@ -103,7 +103,7 @@ groupnorm_stats_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
 }
 
 template <bool kBf16>
-__global__ void __launch_bounds__(kMaxThreads)
+__global__ void __launch_bounds__(kMaxThreads, 4)   // four resident blocks: the grid is sized as one such wave
 groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int groups,
                        int rows_per_chunk, int stat_chunks, const float* __restrict__ partial,
                        const void* __restrict__ gamma, const void* __restrict__ beta, int gb_dtype,
@@ -183,12 +183,10 @@ groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
     return make_uint4(w[0], w[1], w[2], w[3]);
   };
   int64_t r = r0 + ty;
-  for (; r + 3 * k < r1; r += 4 * k) {          // four rows in flight per thread
-    uint4 v[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) v[u] = __ldg(src + (r + u * k) * vec_cols);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) dst[(r + u * k) * vec_cols] = transform(v[u]);
+  for (; r + k < r1; r += 2 * k) {              // two rows in flight per thread
+    const uint4 v0 = __ldg(src + r * vec_cols), v1 = __ldg(src + (r + k) * vec_cols);
+    dst[r * vec_cols] = transform(v0);
+    dst[(r + k) * vec_cols] = transform(v1);
   }
   for (; r < r1; r += k) dst[r * vec_cols] = transform(__ldg(src + r * vec_cols));
 }
