@@ -817,7 +817,8 @@ def run_one_shape(args):
         # `--launches` eager (un-graphed) forward passes of the full-size UNet of configs[3], so
         # that a profiler's launch list shows every kernel of a denoise step by name.
         mm = importlib.import_module(PKG + ".multimesh")
-        unet, _ = mm.build_texture_unet(dev, torch.bfloat16, args.quant, seed=0, init_on_device=True)
+        unet, _ = mm.build_texture_unet(dev, torch.bfloat16, args.quant, seed=0, init_on_device=True,
+                                        fused_gn=False if args.torch_groupnorm else None)
         lat, cond, uncond = mm.mesh_inputs(0, device=dev)
         x = torch.cat([lat, lat]); c = torch.cat([uncond, cond])
         t = torch.full((12,), 500, device=dev)
@@ -988,6 +989,8 @@ def main():
     ap.add_argument("--kernel", default="dense", help="one_shape: dense | sparse | quant | lnquant | prune | fused | groupnorm (shape = B x HW x C) | unet (eager UNet forwards)")
     ap.add_argument("--shape", default="8192x1280x1280", help="one_shape: MxKxN")
     ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--torch-groupnorm", action="store_true",
+                    help="one_shape --kernel unet: keep torch's GroupNorm / SiLU ops instead of the channels-last kernel")
     ap.add_argument("--cpu-frac", type=float, default=None,
                     help="row fraction of each shape timed on the CPU (default: all rows, fewer when "
                          "the requested number of reference passes would take more than ~2 minutes)")
