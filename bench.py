@@ -359,6 +359,22 @@ def measured_denominators(ctx: Ctx):
         out[name] = round(moved / (best * 1e-3) / 1e9, 1) if best else None
     del a, b
     torch.cuda.empty_cache()
+    # tensor memory -> registers: 16 warps per SM, two tcgen05.ld 32x32b.x16 in flight per warp
+    moved = ctypes.c_int64(0)
+    best = None
+    for rep in range(4):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        st = lib.hy3d_probe_tmem_ld(16, 2, 10000, ctypes.byref(moved), cur)
+        e1.record()
+        torch.cuda.synchronize()
+        if st != 0:
+            best = None
+            break
+        if rep:
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+    out["tmem_to_registers_tbs"] = round(moved.value / (best * 1e-3) / 1e12, 1) if best else None
     out["how"] = ("tcgen05.mma kind::i8 128x256x32 (sparse: 128x240x64) on resident operands, 4000 groups of 4 per SM, "
                   "best of 3; 1 GiB streams with 16-byte accesses from 592 CTAs, best of 3")
     return out
