@@ -62,13 +62,13 @@ SIGNATURES = {
     "hy3d_probe_mma_i8": [c_int, c_int, c_int, c_void_p, c_void_p],
     "hy3d_probe_hbm": [c_int, c_void_p, c_void_p, c_int64, c_void_p],
     "hy3d_probe_tmem_ld": [c_int, c_int, c_int, c_void_p, c_void_p],
-    "hy3d_groupnorm_nhwc": [c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int,
-                            ctypes.c_float, c_int, c_void_p, c_void_p, c_void_p],
+    "hy3d_groupnorm_nhwc": [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
+                            c_int, ctypes.c_float, c_int, c_void_p, c_void_p, c_void_p],
     "hy3d_version": [],
 }
 
 # The argument lists above belong to this ABI version of the library (hy3d_version()).
-ABI_VERSION = 200
+ABI_VERSION = 201
 
 
 def configure(lib: ctypes.CDLL) -> ctypes.CDLL:
@@ -187,15 +187,20 @@ class _Base:
                 "hy3d_layernorm_quantize")
         return (q, s, y) if return_normalised else (q, s)
 
-    def groupnorm_nhwc(self, x, groups, gamma, beta, eps, silu=False, out=None, workspace=None):
+    def groupnorm_nhwc(self, x, groups, gamma, beta, eps, silu=False, out=None, workspace=None, add=None):
         """GroupNorm (+ SiLU) of a channels_last (B, C, H, W) f16/bf16 tensor; the result has
         the same shape and memory format.  ``workspace``: optional fp32 tensor of at least
-        ``groupnorm_workspace_floats(B, H*W, groups)`` elements (allocated when absent)."""
+        ``groupnorm_workspace_floats(B, H*W, groups)`` elements (allocated when absent).
+        ``add``: optional (B, C) tensor of x's dtype added per sample and channel first."""
         if x.dim() != 4 or x.dtype not in (torch.float16, torch.bfloat16) or not x.is_cuda:
             raise RuntimeError("groupnorm_nhwc: x must be a 4-D f16/bf16 CUDA tensor")
         if not x.is_contiguous(memory_format=torch.channels_last):
             raise RuntimeError("groupnorm_nhwc: x must be in channels_last memory format")
         B, C, H, W = x.shape
+        if add is not None:
+            if tuple(add.shape) != (B, C) or add.dtype != x.dtype or not add.is_cuda:
+                raise RuntimeError(f"groupnorm_nhwc: add must be a ({B}, {C}) CUDA tensor of {x.dtype}")
+            add = add.contiguous()
         y = out if out is not None else torch.empty_like(x, memory_format=torch.channels_last)
         need = self._lib.hy3d_groupnorm_workspace_floats(B, H * W, groups)
         if workspace is None or workspace.numel() < need:
@@ -206,7 +211,7 @@ class _Base:
         code = _DTYPE_CODE[gb.dtype] if gb is not None else F32
         with torch.cuda.device(x.device):
             self._check(self._lib.hy3d_groupnorm_nhwc(
-                x.data_ptr(), _DTYPE_CODE[x.dtype], B, H * W, C, groups,
+                x.data_ptr(), add.data_ptr() if add is not None else None, _DTYPE_CODE[x.dtype], B, H * W, C, groups,
                 gamma.data_ptr() if gamma is not None else None,
                 beta.data_ptr() if beta is not None else None, code, float(eps), 1 if silu else 0,
                 y.data_ptr(), workspace.data_ptr(), self._stream(x)), "hy3d_groupnorm_nhwc")

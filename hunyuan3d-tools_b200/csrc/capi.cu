@@ -173,12 +173,12 @@ int hy3d_last_device_status(int* status_out) {
   return HY3D_OK;
 }
 
-int hy3d_groupnorm_nhwc(const void* x, int x_dtype, int64_t B, int64_t HW, int64_t C, int groups,
-                        const void* gamma, const void* beta, int gb_dtype, float eps, int silu,
-                        void* y, float* workspace, void* stream) {
+int hy3d_groupnorm_nhwc(const void* x, const void* add, int x_dtype, int64_t B, int64_t HW, int64_t C,
+                        int groups, const void* gamma, const void* beta, int gb_dtype, float eps,
+                        int silu, void* y, float* workspace, void* stream) {
   const int rc = check_device();
   if (rc != HY3D_OK) return rc;
-  return gnorm::groupnorm_nhwc(x, x_dtype, B, HW, C, groups, gamma, beta, gb_dtype, eps, silu, y,
+  return gnorm::groupnorm_nhwc(x, add, x_dtype, B, HW, C, groups, gamma, beta, gb_dtype, eps, silu, y,
                                workspace, static_cast<cudaStream_t>(stream));
 }
 

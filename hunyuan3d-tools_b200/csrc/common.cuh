@@ -11,7 +11,7 @@
 
 #include "../../include/hy3d_int8.h"
 
-#define HY3D_ABI_VERSION 200
+#define HY3D_ABI_VERSION 201
 
 namespace hy3d {
 

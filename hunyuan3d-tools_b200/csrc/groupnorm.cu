@@ -40,14 +40,31 @@ __device__ __forceinline__ void unpack8f(const uint4& v, float (&f)[8]) {
   }
 }
 
+// x + add[b, c], rounded to the activation type as a separate broadcast add would have stored it.
+template <bool kBf16>
+__device__ __forceinline__ void add_round8(float (&f)[8], const float (&a)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; j += 2) {
+    const uint32_t p = pack2(f[j] + a[j], f[j + 1] + a[j + 1], kBf16 ? HY3D_BF16 : HY3D_F16);
+    if (kBf16) {
+      f[j] = __uint_as_float(p << 16);
+      f[j + 1] = __uint_as_float(p & 0xFFFF0000u);
+    } else {
+      const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&p));
+      f[j] = t.x;
+      f[j + 1] = t.y;
+    }
+  }
+}
+
 // Threads are laid out as (row lane ty, vector column tx): tx = tid % (C/8) owns 8 adjacent
 // channels, ty = tid / (C/8) walks rows ty, ty + k, ...  blockDim.x = (C/8) * k.
 //
 // partial layout: [B][chunks][groups][2] floats (sum, sum of squares).
-template <bool kBf16>
-__global__ void __launch_bounds__(kMaxThreads)
-groupnorm_stats_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int groups,
-                       int rows_per_chunk, float* __restrict__ partial) {
+template <bool kBf16, bool kAdd>
+__global__ void __launch_bounds__(kMaxThreads, kAdd ? 4 : 0)
+groupnorm_stats_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ add, int64_t HW, int C,
+                       int groups, int rows_per_chunk, float* __restrict__ partial) {
   extern __shared__ float s_acc[];          // [k][2][C]: per row lane, per-channel sum / sum of squares
   pdl_launch_dependents();
   const int vec_cols = C >> 3;
@@ -57,9 +74,10 @@ groupnorm_stats_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
   const int64_t r0 = static_cast<int64_t>(chunk) * rows_per_chunk;
   const int64_t r1 = r0 + rows_per_chunk < HW ? r0 + rows_per_chunk : HW;
   pdl_wait();
-  float s[8], q[8];
+  float s[8], q[8], av[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) { s[j] = 0.0f; q[j] = 0.0f; }
+  for (int j = 0; j < 8; ++j) { s[j] = 0.0f; q[j] = 0.0f; av[j] = 0.0f; }
+  if (kAdd) unpack8f<kBf16>(__ldg(reinterpret_cast<const uint4*>(add + static_cast<int64_t>(b) * C) + tx), av);
   const uint4* base = reinterpret_cast<const uint4*>(x + (static_cast<int64_t>(b) * HW) * C) + tx;
   int64_t r = r0 + ty;
   // four rows in flight per thread
@@ -71,6 +89,7 @@ groupnorm_stats_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
     for (int u = 0; u < 4; ++u) {
       float f[8];
       unpack8f<kBf16>(v[u], f);
+      if (kAdd) add_round8<kBf16>(f, av);
 #pragma unroll
       for (int j = 0; j < 8; ++j) { s[j] += f[j]; q[j] = fmaf(f[j], f[j], q[j]); }
     }
@@ -78,6 +97,7 @@ groupnorm_stats_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
   for (; r < r1; r += k) {
     float f[8];
     unpack8f<kBf16>(__ldg(base + r * vec_cols), f);
+    if (kAdd) add_round8<kBf16>(f, av);
 #pragma unroll
     for (int j = 0; j < 8; ++j) { s[j] += f[j]; q[j] = fmaf(f[j], f[j], q[j]); }
   }
@@ -102,9 +122,9 @@ groupnorm_stats_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
   }
 }
 
-template <bool kBf16>
+template <bool kBf16, bool kAdd>
 __global__ void __launch_bounds__(kMaxThreads, 4)   // four resident blocks: the grid is sized as one such wave
-groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int groups,
+groupnorm_apply_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ add, int64_t HW, int C, int groups,
                        int rows_per_chunk, int stat_chunks, const float* __restrict__ partial,
                        const void* __restrict__ gamma, const void* __restrict__ beta, int gb_dtype,
                        float eps, int silu, uint16_t* __restrict__ y) {
@@ -149,9 +169,10 @@ groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
     s_ab[C + c] = fmaf(-mean, rstd * ga, be);
   }
   __syncthreads();
-  float sc[8], sh[8];
+  float sc[8], sh[8], av[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) { sc[j] = s_ab[8 * tx + j]; sh[j] = s_ab[C + 8 * tx + j]; }
+  for (int j = 0; j < 8; ++j) { sc[j] = s_ab[8 * tx + j]; sh[j] = s_ab[C + 8 * tx + j]; av[j] = 0.0f; }
+  if (kAdd) unpack8f<kBf16>(__ldg(reinterpret_cast<const uint4*>(add + static_cast<int64_t>(b) * C) + tx), av);
   const int64_t r0 = static_cast<int64_t>(chunk) * rows_per_chunk;
   const int64_t r1 = r0 + rows_per_chunk < HW ? r0 + rows_per_chunk : HW;
   const int64_t sample = (static_cast<int64_t>(b) * HW) * C;
@@ -160,6 +181,7 @@ groupnorm_apply_kernel(const uint16_t* __restrict__ x, int64_t HW, int C, int gr
   auto transform = [&](const uint4& v) {
     float f[8];
     unpack8f<kBf16>(v, f);
+    if (kAdd) add_round8<kBf16>(f, av);
     uint32_t w[4];
 #pragma unroll
     for (int j = 0; j < 8; j += 2) {
@@ -211,7 +233,7 @@ int64_t workspace_floats(int64_t B, int64_t HW, int groups) {
   return B * chunks_for(B, HW) * groups * 2;
 }
 
-int groupnorm_nhwc(const void* x, int x_dtype, int64_t B, int64_t HW, int64_t C, int groups,
+int groupnorm_nhwc(const void* x, const void* add, int x_dtype, int64_t B, int64_t HW, int64_t C, int groups,
                    const void* gamma, const void* beta, int gb_dtype, float eps, int silu,
                    void* y, float* workspace, cudaStream_t stream) {
   if (x_dtype != HY3D_F16 && x_dtype != HY3D_BF16) return HY3D_ERR_ARG;
@@ -220,7 +242,8 @@ int groupnorm_nhwc(const void* x, int x_dtype, int64_t B, int64_t HW, int64_t C,
   if (C > 8 * kMaxThreads || B > 65535 || HW > (1ll << 31)) return HY3D_ERR_SHAPE;
   if (B == 0) return HY3D_OK;
   if (!x || !y || !workspace) return HY3D_ERR_ARG;
-  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) return HY3D_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(add)) & 15)
+    return HY3D_ERR_SHAPE;
   const int Ci = static_cast<int>(C);
   const int vec_cols = Ci >> 3;
   const int k = kMaxThreads / vec_cols > 0 ? kMaxThreads / vec_cols : 1;
@@ -233,6 +256,7 @@ int groupnorm_nhwc(const void* x, int x_dtype, int64_t B, int64_t HW, int64_t C,
   const bool bf16 = x_dtype == HY3D_BF16;
   const uint16_t* xp = static_cast<const uint16_t*>(x);
   uint16_t* yp = static_cast<uint16_t*>(y);
+  const uint16_t* ap = static_cast<const uint16_t*>(add);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(chunks), static_cast<unsigned>(B));
   cfg.blockDim = dim3(static_cast<unsigned>(threads));
@@ -244,13 +268,20 @@ int groupnorm_nhwc(const void* x, int x_dtype, int64_t B, int64_t HW, int64_t C,
   cfg.numAttrs = 1;
   cudaError_t err;
   cfg.dynamicSmemBytes = smem_stats;
-  if (bf16) err = cudaLaunchKernelEx(&cfg, groupnorm_stats_kernel<true>, xp, HW, Ci, groups, rows_per_chunk, workspace);
-  else err = cudaLaunchKernelEx(&cfg, groupnorm_stats_kernel<false>, xp, HW, Ci, groups, rows_per_chunk, workspace);
+#define HY3D_GN_STATS(BF, AD) \
+  err = cudaLaunchKernelEx(&cfg, groupnorm_stats_kernel<BF, AD>, xp, ap, HW, Ci, groups, rows_per_chunk, workspace)
+  if (bf16) { if (ap) HY3D_GN_STATS(true, true); else HY3D_GN_STATS(true, false); }
+  else { if (ap) HY3D_GN_STATS(false, true); else HY3D_GN_STATS(false, false); }
+#undef HY3D_GN_STATS
   if (err != cudaSuccess) { cudaGetLastError(); return HY3D_ERR_CUDA; }
   const float* ws = workspace;
   cfg.dynamicSmemBytes = smem;
-  if (bf16) err = cudaLaunchKernelEx(&cfg, groupnorm_apply_kernel<true>, xp, HW, Ci, groups, rows_per_chunk, chunks, ws, gamma, beta, gb_dtype, eps, silu, yp);
-  else err = cudaLaunchKernelEx(&cfg, groupnorm_apply_kernel<false>, xp, HW, Ci, groups, rows_per_chunk, chunks, ws, gamma, beta, gb_dtype, eps, silu, yp);
+#define HY3D_GN_APPLY(BF, AD)                                                                       \
+  err = cudaLaunchKernelEx(&cfg, groupnorm_apply_kernel<BF, AD>, xp, ap, HW, Ci, groups, rows_per_chunk, \
+                           chunks, ws, gamma, beta, gb_dtype, eps, silu, yp)
+  if (bf16) { if (ap) HY3D_GN_APPLY(true, true); else HY3D_GN_APPLY(true, false); }
+  else { if (ap) HY3D_GN_APPLY(false, true); else HY3D_GN_APPLY(false, false); }
+#undef HY3D_GN_APPLY
   if (err != cudaSuccess) { cudaGetLastError(); return HY3D_ERR_CUDA; }
   return HY3D_OK;
 }

@@ -46,7 +46,9 @@ class GroupNormNHWC(nn.GroupNorm):
         self._ik = None
         self._ws = None
 
-    def forward(self, x):
+    def forward(self, x, add=None):
+        """``add``: optional (B, C) term added to every pixel before the normalisation (the
+        time-embedding projection of a ResNet block); the kernel path adds it on the fly."""
         if (self.fused and x.is_cuda and x.dim() == 4 and x.dtype in (torch.float16, torch.bfloat16)
                 and x.is_contiguous(memory_format=torch.channels_last)):
             if self._ik is None:
@@ -55,7 +57,10 @@ class GroupNormNHWC(nn.GroupNorm):
             if self._ws is None or self._ws.device != x.device:
                 self._ws = torch.empty(1 << 16, dtype=torch.float32, device=x.device)
             return self._ik.groupnorm_nhwc(x, self.num_groups, self.weight, self.bias, self.eps,
-                                           silu=self.silu, workspace=self._ws)
+                                           silu=self.silu, workspace=self._ws,
+                                           add=None if add is None else add.to(x.dtype))
+        if add is not None:
+            x = x + add[:, :, None, None]
         y = super().forward(x)
         return F.silu(y) if self.silu else y
 
@@ -72,8 +77,8 @@ class ResnetBlock(nn.Module):
 
     def forward(self, x, temb):
         h = self.conv1(self.norm1(x))              # GroupNorm + SiLU
-        h = h + self.time_emb_proj(F.silu(temb))[:, :, None, None]
-        h = self.conv2(self.norm2(h))
+        # h + time embedding feeds norm2 only, so the broadcast add rides in the normalisation
+        h = self.conv2(self.norm2(h, add=self.time_emb_proj(F.silu(temb))))
         if self.conv_shortcut is not None:
             x = self.conv_shortcut(x)
         return x + h

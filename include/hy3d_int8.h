@@ -103,14 +103,17 @@ int hy3d_layernorm_quantize(const void* x, int x_dtype, int64_t M, int64_t K, in
  * with silu != 0 the rounded value v becomes v / (1 + exp(-v)), rounded again.  gamma / beta:
  * (C) of gb_dtype or NULL.  workspace: hy3d_groupnorm_workspace_floats(B, HW, groups) floats of
  * device memory owned by the caller (per-chunk partial sums; no initialisation needed).
- * Requires C % 8 == 0, C % groups == 0, C <= 2560, 16-byte aligned x and y.  y may equal x.
+ * add: optional (B, C) array of x_dtype added to every pixel of its sample before the
+ * normalisation -- x + add[b, c] rounded to x_dtype, as a separate broadcast add would store it
+ * (a UNet's time-embedding term) -- or NULL.
+ * Requires C % 8 == 0, C % groups == 0, C <= 2560, 16-byte aligned x, y and add.  y may equal x.
  * Replaces nothing in the reference (its UNet normalises with stock PyTorch); it serves the
  * model around the INT8 layers, whose convolutions run NHWC while torch's GroupNorm kernel
  * takes NCHW only and so costs two layout copies per call.
  */
-int hy3d_groupnorm_nhwc(const void* x, int x_dtype, int64_t B, int64_t HW, int64_t C, int groups,
-                        const void* gamma, const void* beta, int gb_dtype, float eps, int silu,
-                        void* y, float* workspace, void* stream);
+int hy3d_groupnorm_nhwc(const void* x, const void* add, int x_dtype, int64_t B, int64_t HW, int64_t C,
+                        int groups, const void* gamma, const void* beta, int gb_dtype, float eps,
+                        int silu, void* y, float* workspace, void* stream);
 int64_t hy3d_groupnorm_workspace_floats(int64_t B, int64_t HW, int groups);
 
 /*

@@ -426,6 +426,16 @@ def test_groupnorm_nhwc_matches_torch_fp32(ik, dtype, silu, shape):
     x2 = x.clone(memory_format=torch.channels_last)
     ik.groupnorm_nhwc(x2, 32, gamma, beta, 1e-5, silu=silu, out=x2)
     assert torch.equal(x2, y)
+    # with a per-(sample, channel) term added first, rounded as a separate add would store it
+    add = (torch.randn(B, C, generator=g) * 0.5).to(dtype).to(DEV)
+    ya = ik.groupnorm_nhwc(x, 32, gamma, beta, 1e-5, silu=silu, add=add)
+    xa = (x + add[:, :, None, None])
+    refa = torch.nn.functional.group_norm(xa.float(), 32, gamma.float(), beta.float(), 1e-5).to(dtype)
+    if silu:
+        refa = torch.nn.functional.silu(refa.float()).to(dtype)
+    assert O.rel_l2(ya, refa) < (3e-3 if dtype == torch.bfloat16 else 4e-4)
+    ulpa = (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10) * float(refa.float().abs().max())
+    assert float((ya.float() - refa.float()).abs().max()) <= 2 * ulpa
 
 
 def test_groupnorm_nhwc_argument_checks(ik):
