@@ -2,10 +2,13 @@
 //
 // One persistent CTA per SM walks 128 x block_n output tiles.  Roles by warp:
 //   warp 0      TMA producer: A (128 x 128 B) and B (block_n x 128 B) boxes, 128-byte swizzle,
-//               into a ring of shared-memory stages, signalled through "full" mbarriers.
-//   warp 1      owns tensor memory; one thread issues tcgen05.mma kind::i8
-//               (128 x block_n x 32 per instruction, int32 accumulators in tensor memory) and
-//               commits each stage back to its "empty" mbarrier.
+//               into a ring of shared-memory stages, signalled through "full" mbarriers.  Where
+//               the CTA keeps one tile column and its B tile fits, B is loaded once and stays
+//               resident; only A streams.
+//   warp 1      owns tensor memory; issues tcgen05.mma kind::i8 (128 x block_n x 32 per
+//               instruction, int32 accumulators in tensor memory) and commits each stage back
+//               to its "empty" mbarrier.
+//               Both of these run as warp-uniform loops: all lanes wait and count, lane 0 issues.
 //   warps 2-17  epilogue, four warps per 32-lane quarter of tensor memory, alternating over
 //               32-column slabs: tcgen05.ld, acc * (act_scale[m] * w_scale[n]) + bias[n],
 //               optional GELU / GEGLU, pack to bf16 / fp16 into a 64-byte-swizzled staging
@@ -52,7 +55,7 @@ struct DenseArgs {
   int b_resident;  // the CTA's B tile (all K blocks) is loaded once and stays in shared memory
   int m_tiles, n_tiles, num_kb, last_ksteps, n_fastest;
   int atoms;   // 128-byte K blocks per pipeline stage (1 or 2)
-  int debug;   // knock-out switches of -DHY3D_TRACE builds (always 0 in the shipped library)
+  int debug;   // knock-out switches of -DHY3D_TRACE / -DHY3D_KO diagnostic builds (always 0 in the shipped library)
 };
 
 struct __align__(16) DenseCtrl {
