@@ -36,6 +36,28 @@ __device__ __forceinline__ uint32_t prune_group(const int (&v)[4], int& k0, int&
   return static_cast<uint32_t>(idx0 | (idx1 << 2));
 }
 
+// The same selection without branches or indexed arrays, on the four bytes of one word: the
+// dropped pair are the two smallest keys (|v|, index) -- the strict comparisons above keep the
+// later element on ties, i.e. order equal magnitudes by index -- so element i survives iff at
+// least two keys are smaller than its own.  Returns the nibble; `two` receives the survivors
+// (ascending index) in its low 16 bits.
+__device__ __forceinline__ uint32_t prune_word(uint32_t w, uint32_t& two) {
+  const uint32_t a = __vabs4(w);                      // |v| per byte as unsigned (|-128| = 128)
+  const uint32_t a0 = a & 0xFFu, a1 = (a >> 8) & 0xFFu, a2 = (a >> 16) & 0xFFu, a3 = a >> 24;
+  // c_ij (i < j): key_i < key_j  <=>  a_i <= a_j
+  const uint32_t c01 = a0 <= a1, c02 = a0 <= a2, c03 = a0 <= a3;
+  const uint32_t c12 = a1 <= a2, c13 = a1 <= a3, c23 = a2 <= a3;
+  const uint32_t r0 = 3u - c01 - c02 - c03;           // number of smaller keys
+  const uint32_t r1 = 2u + c01 - c12 - c13;
+  const uint32_t r2 = 1u + c02 + c12 - c23;
+  const uint32_t r3 = c03 + c13 + c23;
+  const uint32_t keep = (r0 >> 1) | ((r1 >> 1) << 1) | ((r2 >> 1) << 2) | ((r3 >> 1) << 3);
+  const uint32_t idx0 = static_cast<uint32_t>(__ffs(static_cast<int>(keep)) - 1);
+  const uint32_t idx1 = 31u - static_cast<uint32_t>(__clz(static_cast<int>(keep)));
+  two = __byte_perm(w, 0u, idx0 | (idx1 << 4)) & 0xFFFFu;
+  return idx0 | (idx1 << 2);
+}
+
 __device__ __forceinline__ void unpack4(uint32_t w, int (&v)[4]) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) v[i] = static_cast<int>(static_cast<int8_t>((w >> (8 * i)) & 0xFF));
@@ -63,12 +85,10 @@ prune_pack_kernel(const int8_t* __restrict__ w, int64_t N, int K, int8_t* __rest
   uint32_t raw[2] = {0, 0};
 #pragma unroll
   for (int g = 0; g < 8; ++g) {
-    int v[4], k0, k1;
-    unpack4(words[g], v);
-    const uint32_t nib = prune_group(v, k0, k1);
+    uint32_t two;
+    const uint32_t nib = prune_word(words[g], two);
     packed |= nib << (4 * g);
     raw[g >> 2] |= nib << (8 * (g & 3));
-    const uint32_t two = (static_cast<uint32_t>(k0) & 0xFF) | ((static_cast<uint32_t>(k1) & 0xFF) << 8);
     out[g >> 1] |= two << (16 * (g & 1));
   }
   *reinterpret_cast<uint4*>(comp + row * (K >> 1) + (chunk << 4)) =
