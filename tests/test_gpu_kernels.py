@@ -114,6 +114,36 @@ def test_dense_accumulators_bit_exact(tc, M, K, N, bn):
 
 
 @pytest.mark.parametrize("M,K,N,bn", [
+    (40000, 192, 256, 0),     # one tile column, 313 row tiles (last one ragged), two K blocks
+    (38000, 320, 640, 0),     # three columns of 224; ragged last K block
+    (37900, 640, 160, 160),   # five K blocks resident
+    (40000, 320, 2560, 256),  # ten columns
+])
+def test_dense_resident_b_tile_bit_exact(tc, M, K, N, bn):
+    """Launches that keep one tile column per CTA with at least two tiles each load their B tile
+    once and stream only A (single-CTA tiles; K = 192 / 320 / 640 with two, three and five K
+    blocks, ragged last row tile, ragged last K block, one and several tile columns)."""
+    A, B = _rand_i8((M, K), M + K + 5), _rand_i8((N, K), N + K + 6)
+    acc = tc.int8_gemm_tc(A.to(DEV), B.to(DEV), None, None, None, out_dtype=torch.int32,
+                          cta_group=1, block_n=bn)
+    assert torch.equal(acc.cpu(), O.int32_matmul(A, B))
+    g = torch.Generator().manual_seed(M)
+    a_s = torch.rand(M, generator=g) * 0.05 + 1e-3
+    w_s = (torch.rand(N, generator=g) * 1e-3 + 1e-5).bfloat16()
+    bias = (torch.randn(N, generator=g) * 0.1).bfloat16()
+    y = tc.int8_gemm_tc(A.to(DEV), B.to(DEV), a_s.to(DEV), w_s.to(DEV), bias.to(DEV),
+                        out_dtype=torch.bfloat16, cta_group=1, block_n=bn)
+    ref = O.epilogue(O.int32_matmul(A, B), a_s, w_s, bias, torch.bfloat16, "linear")
+    assert O.rel_l2(y, ref) < 2e-3          # same accumulators and formula; fma contraction only
+    # and the resident-B launch equals the streaming one bit for bit (pairs stream both operands)
+    if K >= 64 and N % 32 == 0:
+        y2 = tc.int8_gemm_tc(A.to(DEV), B.to(DEV), a_s.to(DEV), w_s.to(DEV), bias.to(DEV),
+                             out_dtype=torch.bfloat16, cta_group=2, block_n=bn)
+        assert torch.equal(y, y2)
+    assert tc.device_status() == 0
+
+
+@pytest.mark.parametrize("M,K,N,bn", [
     (2600, 2064, 512, 0),     # K = 8 deep stages + a 16-element tail; ragged last row tile
     (300, 1024, 256, 256),    # exactly four deep stages, second CTA's rows half empty
     (1000, 1104, 320, 160),   # tail of 80: three K steps of the first block
