@@ -430,7 +430,8 @@ def test_layernorm_quantize_without_affine_and_argument_checks(ik):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("silu", [False, True])
 @pytest.mark.parametrize("shape", [(2, 320, 32, 32), (3, 640, 16, 16), (2, 960, 16, 16), (1, 1280, 8, 8),
-                                   (2, 2560, 8, 8), (1, 64, 5, 7), (12, 320, 64, 64)])
+                                   (2, 2560, 8, 8), (1, 64, 5, 7), (12, 320, 64, 64),
+                                   (300, 64, 4, 4), (700, 64, 3, 5)])   # more samples than one wave of blocks
 def test_groupnorm_nhwc_matches_torch_fp32(ik, dtype, silu, shape):
     """The channels-last GroupNorm (+ SiLU) kernel against torch's ops on the same values:
     fp32 group_norm, rounded to the activation type, then (optionally) fp32 SiLU of the rounded
