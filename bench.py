@@ -429,6 +429,15 @@ def per_shape_table(ctx: Ctx, shapes):
         r["gemm_dense_us"] = graph_us([lambda s, i=i: ck(lib.hy3d_gemm_w8a8_dense(
             qs[i].data_ptr(), ws[i].data_ptr(), ss[i].data_ptr(), wsc.data_ptr(), 1, bias.data_ptr(), 1,
             outs[i].data_ptr(), 1, M, N, K, 0, 0, 0, s)) for i in range(R)])
+        import ctypes
+        wsb = ctypes.c_int64(0)
+        planned = lib.hy3d_dense_splitk_plan(M, N, K, 0, ctypes.byref(wsb))
+        if planned > 1:     # few rows, deep K: K ranges side by side + reduce / epilogue kernel
+            part = torch.empty(wsb.value // 4, dtype=torch.int32, device=dev)
+            r["gemm_dense_splitk_us"] = graph_us([lambda s, i=i: ck(lib.hy3d_gemm_w8a8_dense_splitk(
+                qs[i].data_ptr(), ws[i].data_ptr(), ss[i].data_ptr(), wsc.data_ptr(), 1, bias.data_ptr(), 1,
+                outs[i].data_ptr(), 1, M, N, K, 0, planned, part.data_ptr(), wsb.value, s)) for i in range(R)])
+            r["splitk_ranges"] = planned
         r["layer_dense_us"] = graph_us([lambda s, i=i: ck(lib.hy3d_linear_w8a8_dense(
             xs[i].data_ptr(), 1, K, qs[i].data_ptr(), ss[i].data_ptr(), ws[i].data_ptr(), wsc.data_ptr(), 1,
             bias.data_ptr(), 1, outs[i].data_ptr(), 1, M, N, K, 0, 0, 0, s)) for i in range(R)])

@@ -34,6 +34,9 @@ SIGNATURES = {
     "hy3d_gemm_w8a8_dense": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                              c_void_p, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int,
                              c_void_p],
+    "hy3d_dense_splitk_plan": [c_int64, c_int64, c_int64, c_int, c_void_p],
+    "hy3d_gemm_w8a8_dense_splitk": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                    c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p],
     "hy3d_linear_w8a8_dense": [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64,
                                c_int, c_int, c_int, c_void_p],
@@ -265,11 +268,18 @@ class Int8KernelsModule(_Base):
 class TcGemmModule(_Base):
     """Counterpart of the reference's ``int8_gemm_tc`` extension (csrc/int8_gemm_tc.cu)."""
 
+    def dense_splitk_plan(self, M, N, K, epilogue=EPI_LINEAR):
+        """(K ranges this library would use for the shape -- 1 = no split --, workspace bytes)."""
+        nbytes = ctypes.c_int64(0)
+        splits = self._lib.hy3d_dense_splitk_plan(M, N, K, epilogue, ctypes.byref(nbytes))
+        return int(splits), int(nbytes.value)
+
     def int8_gemm_tc(self, A, B, act_scale, w_scale, bias, out_dtype=None, epilogue=EPI_LINEAR,
-                     cta_group=0, block_n=0):
+                     cta_group=0, block_n=0, splits=None):
         """A (M,K) s8, B (N,K) s8, act_scale (M) f32, w_scale (N), bias (N) or empty ->
         (M,N).  csrc/int8_gemm_tc.cu:254-309.  ``out_dtype=torch.int32`` returns the raw
-        accumulators."""
+        accumulators.  ``splits``: K ranges of the split-K form (None = the library's plan for
+        the shape, 1 = never split); the result is the same bit for bit."""
         self._req(A, "A", torch.int8, 2)
         self._req(B, "B", torch.int8, 2)
         M, K = A.shape
@@ -280,6 +290,18 @@ class TcGemmModule(_Base):
             out_dtype = w_scale.dtype if w_scale.dtype != torch.float32 else torch.float16
         out = torch.empty(self._out_shape(M, N, epilogue), dtype=out_dtype, device=A.device)
         bptr, bcode = self._opt_bias(bias)
+        if splits is None:
+            splits = self.dense_splitk_plan(M, N, K, epilogue)[0] if (
+                out_dtype in (torch.float16, torch.bfloat16) and cta_group == 0 and block_n == 0) else 1
+        if splits > 1:
+            ws = torch.empty((splits, (M + 127) // 128 * 128, N), dtype=torch.int32, device=A.device)
+            with torch.cuda.device(A.device):
+                self._check(self._lib.hy3d_gemm_w8a8_dense_splitk(
+                    A.data_ptr(), B.data_ptr(), act_scale.data_ptr(), w_scale.data_ptr(),
+                    _DTYPE_CODE[w_scale.dtype], bptr, bcode, out.data_ptr(), _DTYPE_CODE[out_dtype],
+                    M, N, K, epilogue, splits, ws.data_ptr(), ws.numel() * 4, self._stream(A)),
+                    "hy3d_gemm_w8a8_dense_splitk")
+            return out
         as_ptr = act_scale.data_ptr() if act_scale is not None else None
         ws_ptr = w_scale.data_ptr() if w_scale is not None else None
         ws_code = _DTYPE_CODE[w_scale.dtype] if w_scale is not None else F32
@@ -327,6 +349,9 @@ class TcGemmModule(_Base):
         N = w_int8.shape[0]
         if w_int8.shape[1] != K:
             raise RuntimeError(f"K mismatch: x has {K}, w_int8 has {w_int8.shape[1]}")
+        if cta_group == 0 and block_n == 0 and self.dense_splitk_plan(M, N, K, epilogue)[0] > 1:
+            q, s = self._quantize(x)                     # few rows, deep K: split-K GEMM
+            return self.int8_gemm_tc(q, w_int8, s, w_scale, bias, out_dtype=x.dtype, epilogue=epilogue)
         q = torch.empty((M, K), dtype=torch.int8, device=x.device)
         s = torch.empty((M,), dtype=torch.float32, device=x.device)
         out = torch.empty(self._out_shape(M, N, epilogue), dtype=x.dtype, device=x.device)

@@ -241,6 +241,29 @@ int hy3d_gemm_w8a8_dense(const int8_t* A, const int8_t* B, const float* act_scal
                     N, K, epilogue, cta_group, block_n, static_cast<cudaStream_t>(stream));
 }
 
+int hy3d_dense_splitk_plan(int64_t M, int64_t N, int64_t K, int epilogue, int64_t* workspace_bytes) {
+  if (check_device() != HY3D_OK) return 1;
+  const int splits = dense_splitk_plan(M, N, K, epilogue);
+  // every K range owns an M-padded (whole 128-row tiles) int32 matrix
+  if (workspace_bytes) *workspace_bytes = splits > 1 ? static_cast<int64_t>(splits) * ((M + 127) / 128 * 128) * N * 4 : 0;
+  return splits;
+}
+
+int hy3d_gemm_w8a8_dense_splitk(const int8_t* A, const int8_t* B, const float* act_scale,
+                                const void* w_scale, int w_scale_dtype, const void* bias,
+                                int bias_dtype, void* out, int out_dtype, int64_t M, int64_t N,
+                                int64_t K, int epilogue, int splits, void* workspace,
+                                int64_t workspace_bytes, void* stream) {
+  const int rc = check_device();
+  if (rc != HY3D_OK) return rc;
+  if (splits < 1 || splits > 64) return HY3D_ERR_ARG;
+  if (splits > 1 && (!workspace || workspace_bytes < static_cast<int64_t>(splits) * ((M + 127) / 128 * 128) * N * 4))
+    return HY3D_ERR_TOO_LARGE;
+  return gemm_dense(A, B, act_scale, w_scale, w_scale_dtype, bias, bias_dtype, out, out_dtype, M,
+                    N, K, epilogue, splits > 1 ? 1 : 0, 0, static_cast<cudaStream_t>(stream), splits,
+                    static_cast<int32_t*>(workspace));
+}
+
 int hy3d_linear_w8a8_dense(const void* x, int x_dtype, int64_t ldx, int8_t* q_ws, float* scale_ws,
                            const int8_t* B, const void* w_scale, int w_scale_dtype,
                            const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M,

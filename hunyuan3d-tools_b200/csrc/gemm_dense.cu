@@ -52,6 +52,10 @@ struct DenseArgs {
   int ws_dtype, bias_dtype, out_dtype, epilogue;
   int M, N, K;
   int block_n, stages, acc_cols, tma_store, store_bufs;
+  int splits;        // split-K: the launch walks total_tiles x splits (tile, K range) units ...
+  int kb_per_split;  // ... of this many pipeline stages each, writing raw int32 partials ...
+  int64_t split_stride;   // ... `split_stride` elements apart behind `out`
+  int m_rows_pad;         // rows of one partial matrix (M rounded up to whole tiles)
   int b_resident;  // the CTA's B tile (all K blocks) is loaded once and stays in shared memory
   int m_tiles, n_tiles, num_kb, last_ksteps, n_fastest;
   int atoms;   // 128-byte K blocks per pipeline stage (1 or 2)
@@ -208,6 +212,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const int total_tiles = p.m_tiles * p.n_tiles;     // m_tiles counts 128*kG-row units
+  // Split-K launches walk (tile, K range) units: unit u = split * total_tiles + tile.
+  const int total_units = total_tiles * p.splits;
   const uint32_t cta_rank = kG == 2 ? cluster_cta_rank() : 0u;
   const bool leader = cta_rank == 0;                 // issues the MMAs for the pair
   // Tile order: M-fastest (CTAs running together share a B tile) or N-fastest (they share an A
@@ -262,7 +268,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      if (b_res && first_tile < total_tiles && issuer) {
+      if (b_res && first_tile < total_units && issuer) {
         const uint32_t bf = smem_u32(&ctrl->b_full);
         const int n0 = tile_n(first_tile) * p.block_n;
         mbar_arrive_expect_tx(bf, b_res_bytes);
@@ -270,10 +276,14 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           tma_load_2d(b_res_base + kb * b_bytes, &tm_b, bf, kb * kBlockKBytes, n0);
       }
       __syncwarp();
-      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step) {
+      for (int unit = first_tile; ok && unit < total_units; unit += tile_step) {
+        const int split = p.splits > 1 ? unit / total_tiles : 0;
+        const int tile = unit - split * total_tiles;
+        const int kb0 = split * p.kb_per_split;
+        const int nkb = p.splits > 1 ? min(p.kb_per_split, p.num_kb - kb0) : p.num_kb;
         const int m0 = tile_m(tile) * (kTileM * kG) + row_off;
         const int n0 = tile_n(tile) * p.block_n + col_off;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = 0; kb < nkb; ++kb) {
           ok = mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag, kDevTimeoutEmpty);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
@@ -303,7 +313,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             mbar_arrive_expect_tx(full, stage_bytes);
 #pragma unroll
             for (int a = 0; a < kAtoms; ++a) {
-              const int kx = (kb * kAtoms + a) * kBlockKBytes;   // past K: zero-filled
+              const int kx = ((kb0 + kb) * kAtoms + a) * kBlockKBytes;   // past K: zero-filled
               tma_load_2d(sa + a * a_bytes, &tm_a, full, kx, m0);
               tma_load_2d(sa + kAtoms * a_bytes + a * b_bytes, &tm_b, full, kx, n0);
             }
@@ -313,7 +323,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             if (leader) mbar_arrive_expect_tx(full, 2 * stage_bytes);
 #pragma unroll
             for (int a = 0; a < kAtoms; ++a) {
-              const int kx = (kb * kAtoms + a) * kBlockKBytes;
+              const int kx = ((kb0 + kb) * kAtoms + a) * kBlockKBytes;
               tma_load_2d_pair(sa + a * a_bytes, &tm_a, full_leader, kx, m0);
               tma_load_2d_pair(sa + kAtoms * a_bytes + a * b_bytes, &tm_b, full_leader, kx, n0);
             }
@@ -347,8 +357,6 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #else
       constexpr bool do_mma = true;
 #endif
-      // stages with the full 4 K steps per 128-byte block
-      const int full_kb = p.last_ksteps == 4 * kAtoms ? p.num_kb : p.num_kb - 1;
       int stage = 0;
       uint32_t phase = 0;
       uint32_t a_lo = a_lo0;
@@ -371,14 +379,18 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         else tc_commit_2cta(smem_u32(&ctrl->empty[stage]), 3);
       };
       const uint32_t b_res_lo0 = lo_const | ((b_res_base & 0x3FFFFu) >> 4);
-      if (b_res && first_tile < total_tiles) {
+      if (b_res && first_tile < total_units) {
         ok = mbar_wait(smem_u32(&ctrl->b_full), 0, abort_flag, kDevTimeoutFull);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after_sync();
       }
-      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_step, ++it) {
+      for (int unit = first_tile; ok && unit < total_units; unit += tile_step, ++it) {
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        // K range of this unit; only the last range of a matrix can end in a ragged stage
+        const int kb0 = p.splits > 1 ? (unit / total_tiles) * p.kb_per_split : 0;
+        const int nkb = p.splits > 1 ? min(p.kb_per_split, p.num_kb - kb0) : p.num_kb;
+        const int full_kb = (kb0 + nkb == p.num_kb && p.last_ksteps != 4 * kAtoms) ? nkb - 1 : nkb;
         ok = mbar_wait(smem_u32(&ctrl->tmem_empty[buf]), acc_phase ^ 1, abort_flag,
                        kDevTimeoutTmemEmpty);
         ok = __all_sync(0xffffffffu, ok);
@@ -435,7 +447,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           acc = 1u;
           next_stage();
         }
-        if (ok && full_kb < p.num_kb) {   // ragged last stage: fewer K steps
+        if (ok && full_kb < nkb) {   // ragged last stage: fewer K steps
           ok = wait_full();
           if (ok) {
             if (issuer) {
@@ -497,19 +509,26 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int fast_dim = p.n_fastest ? p.n_tiles : p.m_tiles;
     const int step_slow = tile_step / fast_dim, step_fast = tile_step - step_slow * fast_dim;
     int t_fast = 0, t_slow = 0;
-    if (first_tile < total_tiles) {
+    if (first_tile < total_tiles && p.splits == 1) {
       t_slow = first_tile / fast_dim;
       t_fast = first_tile - t_slow * fast_dim;
       const int m_first = (p.n_fastest ? t_slow : t_fast) * (kTileM * kG) + row_off + row_in_tile;
       if (scaled && m_first < p.M) as_next = p.act_scale[m_first];
     }
-    for (int tile = first_tile; tile < total_tiles; tile += tile_step, ++it) {
+    for (int tile = first_tile; tile < total_units; tile += tile_step, ++it) {
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      int split = 0;
+      if (p.splits > 1) {   // few tiles per CTA here: plain divisions
+        split = tile / total_tiles;
+        const int tl = tile - split * total_tiles;
+        t_slow = p.n_fastest ? tile_m(tl) : tile_n(tl);
+        t_fast = p.n_fastest ? tile_n(tl) : tile_m(tl);
+      }
       const int m0 = (p.n_fastest ? t_slow : t_fast) * (kTileM * kG) + row_off;
       const int n0 = (p.n_fastest ? t_fast : t_slow) * p.block_n;
       float as = as_next;
-      {
+      if (p.splits == 1) {
         t_fast += step_fast;
         t_slow += step_slow;
         if (t_fast >= fast_dim) { t_fast -= fast_dim; ++t_slow; }
@@ -550,7 +569,29 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #else
       constexpr bool skip_epilogue = false;
 #endif
-      if (p.tma_store && !skip_epilogue) {
+      if (p.splits > 1 && p.tma_store && !skip_epilogue) {
+        // Split-K partials: raw int32 accumulators through the same staging buffers and bulk
+        // stores, a slab being 32 rows x 16 int32 columns (64 bytes per row).  Each K range has
+        // its own M-padded matrix in the workspace, so rows past M land in padding.
+        const int nslab16 = p.block_n >> 4;
+        const int out_row = split * p.m_rows_pad + m0 + quarter * 32;
+        const int pend = p.store_bufs - 1;
+        int sb = 0;
+        for (int s = half; s < nslab16; s += kWarpsPerQuarter) {
+          uint32_t r16[16];
+          __syncwarp();
+          tmem_ld_x16(t_row + 16 * s, r16);
+          tmem_ld_wait();
+          if (s + kWarpsPerQuarter >= nslab16) {
+            tc_fence_before_sync();
+            release_acc(smem_u32(&ctrl->tmem_empty[buf]));
+            arrived = true;
+          }
+          slab_store(r16, stage_buf + sb * kSlabBytes, lane, pend, &tm_o, (n0 + 16 * s) * 4, out_row,
+                     n0 + 16 * s < p.N);
+          if (++sb == p.store_bufs) sb = 0;
+        }
+      } else if (p.tma_store && !skip_epilogue) {
         const int nslab = p.block_n / acc_per_slab;
         const int out_row = m0 + quarter * 32;
         const bool rows_in = out_row < p.M;
@@ -605,7 +646,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if (!row_ok || n >= p.N) {
             // nothing to store for this row / column block
           } else if (p.out_dtype == HY3D_S32) {
-            int4* dst = reinterpret_cast<int4*>(reinterpret_cast<int32_t*>(p.out) +
+            int4* dst = reinterpret_cast<int4*>(reinterpret_cast<int32_t*>(p.out) + split * p.split_stride +
                                                 static_cast<int64_t>(m) * ldo + n);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
@@ -687,12 +728,122 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   }
 }
 
+// Eight consecutive per-column parameters (16-byte aligned start) as floats, one or two vector loads.
+__device__ __forceinline__ void load8_as_float(const void* p, int dtype, int n, float (&f)[8]) {
+  if (dtype == HY3D_F32) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(p) + n));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(p) + n) + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    return;
+  }
+  const uint4 v = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p) + n));
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (dtype == HY3D_BF16) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    } else {
+      const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+}
+
+// Split-K tail: sums the int32 partials of every K range (exact) and applies the layer's
+// epilogue with the formula and roundings of the GEMM kernel's own (acc * (as * ws) + b,
+// optional exact-erf GELU, one rounding to the 16-bit type).  One thread per 8 output columns.
+template <bool kBf16, int kEpi>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const int32_t* __restrict__ partial, int splits, int64_t split_stride,
+                     const float* __restrict__ act_scale, const void* __restrict__ w_scale, int ws_dtype,
+                     const void* __restrict__ bias, int bias_dtype, uint16_t* __restrict__ out,
+                     int64_t M, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int vec_cols = N >> 3;
+  const int64_t total = M * vec_cols;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t m = idx / vec_cols;
+    const int n = static_cast<int>(idx - m * vec_cols) << 3;
+    int acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const int32_t* src = partial + m * N + n;
+    int sidx = 0;
+    for (; sidx + 4 <= splits; sidx += 4) {        // eight independent 16-byte loads in flight
+      int4 lo[4], hi[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        lo[u] = __ldcs(reinterpret_cast<const int4*>(src + (sidx + u) * split_stride));
+        hi[u] = __ldcs(reinterpret_cast<const int4*>(src + (sidx + u) * split_stride) + 1);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        acc[0] += lo[u].x; acc[1] += lo[u].y; acc[2] += lo[u].z; acc[3] += lo[u].w;
+        acc[4] += hi[u].x; acc[5] += hi[u].y; acc[6] += hi[u].z; acc[7] += hi[u].w;
+      }
+    }
+    for (; sidx < splits; ++sidx) {
+      const int4 lo = __ldcs(reinterpret_cast<const int4*>(src + sidx * split_stride));
+      const int4 hi = __ldcs(reinterpret_cast<const int4*>(src + sidx * split_stride) + 1);
+      acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
+      acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
+    }
+    const float as = act_scale[m];
+    float wsf[8], bf[8];
+    load8_as_float(w_scale, ws_dtype, n, wsf);
+    if (bias) {
+      load8_as_float(bias, bias_dtype, n, bf);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) bf[j] = 0.0f;
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      float y[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        y[u] = __fmaf_rn(static_cast<float>(acc[j + u]), __fmul_rn(as, wsf[j + u]), bf[j + u]);
+        if (kEpi == HY3D_EPI_GELU) y[u] = gelu_erf(y[u]);
+      }
+      w[j >> 1] = pack2t<kBf16>(y[0], y[1]);
+    }
+    *reinterpret_cast<uint4*>(out + m * N + n) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 }  // namespace
+
+// Split-K plan for a dense layer: how many K ranges pay (1 = none).  Splitting serves launches
+// whose tiles leave most SMs idle while each tile walks a long K alone (the M = 257 image-encoder
+// layers with K = 6144): the ranges run side by side and a second small kernel adds them up.
+int dense_splitk_plan(int64_t M, int64_t N, int64_t K, int epilogue) {
+  if (epilogue == HY3D_EPI_GEGLU || (N & 7) || M <= 0) return 1;
+  const int sms = device_sm_count() > 0 ? device_sm_count() : 148;
+  const int64_t bn = N <= 128 ? N : 256;
+  const int64_t tiles = ((M + kTileM - 1) / kTileM) * ((N + bn - 1) / bn);
+  const int64_t num_kb = (K + kBlockKBytes - 1) / kBlockKBytes;
+  if (tiles * 2 > sms || num_kb < 16) return 1;
+  // Measured cost model (microseconds): a tile walks its K blocks at ~0.27 us each; every range
+  // writes and re-reads an M-padded int32 matrix at ~5 TB/s; two launches cost ~6 us of fixed
+  // time against ~3.5 us for one.  The split has to win by a tenth to be taken.
+  const double part_us = static_cast<double>((M + kTileM - 1) / kTileM * kTileM) * N * 4.0 * 2.0 / 5.0e6;
+  const double single = num_kb * 0.27 + 3.5;
+  double best = single * 0.9;
+  int best_s = 1;
+  for (int64_t sp = 2; sp <= 16 && sp * tiles <= sms && sp * 4 <= num_kb; ++sp) {
+    const double t = ((num_kb + sp - 1) / sp) * 0.27 + sp * part_us + 6.0;
+    if (t < best) { best = t; best_s = static_cast<int>(sp); }
+  }
+  return best_s;
+}
 
 int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const void* w_scale,
                int ws_dtype, const void* bias, int bias_dtype, void* out, int out_dtype, int64_t M,
                int64_t N, int64_t K, int epilogue, int cta_group, int block_n,
-               cudaStream_t stream) {
+               cudaStream_t stream, int splits = 1, int32_t* workspace = nullptr) {
   if (out_dtype != HY3D_F16 && out_dtype != HY3D_BF16 && out_dtype != HY3D_S32) return HY3D_ERR_ARG;
   if (epilogue < HY3D_EPI_LINEAR || epilogue > HY3D_EPI_GEGLU) return HY3D_ERR_ARG;
   if (out_dtype == HY3D_S32 && epilogue != HY3D_EPI_LINEAR) return HY3D_ERR_ARG;
@@ -705,6 +856,13 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   if (geglu && (N & 31)) return HY3D_ERR_SHAPE;
   if (M == 0) return HY3D_OK;
   if (!A || !B || !out) return HY3D_ERR_ARG;
+  if (splits < 1 || splits > 64) return HY3D_ERR_ARG;
+  if (splits > 1) {
+    // K ranges as int32 partials in the caller's workspace, then the reduce + epilogue kernel.
+    if (!workspace || out_dtype == HY3D_S32 || epilogue == HY3D_EPI_GEGLU || (N & 7)) return HY3D_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 15) || !act_scale || !w_scale) return HY3D_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(w_scale) | reinterpret_cast<uintptr_t>(bias)) & 15) return HY3D_ERR_SHAPE;
+  }
   if (out_dtype != HY3D_S32 && (!act_scale || !w_scale)) return HY3D_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
        reinterpret_cast<uintptr_t>(out)) & 15)
@@ -770,13 +928,26 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   // Deep stages (two 128-byte K blocks, eight MMAs per barrier round trip) for CTA pairs on
   // deep K: a pair's per-stage hand-off crosses the cluster, and halving the number of
   // hand-offs is what lets pairs profit from their smaller shared-memory traffic.
-  const int atoms = (group == 2 && K >= 1024) ? 2 : 1;
+  const int atoms = (group == 2 && K >= 1024 && splits == 1) ? 2 : 1;
   p.atoms = atoms;
   const int stage_k = kBlockKBytes * atoms;
   p.num_kb = static_cast<int>((K + stage_k - 1) / stage_k);
   const int k_last = static_cast<int>(K - static_cast<int64_t>(p.num_kb - 1) * stage_k);
   p.last_ksteps = (k_last + 31) / 32;
+  p.splits = 1; p.kb_per_split = p.num_kb; p.split_stride = 0;
+  const int final_dtype = out_dtype, final_epilogue = epilogue;
+  void* final_out = out;
+  if (splits > 1) {
+    p.kb_per_split = (p.num_kb + splits - 1) / splits;
+    splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;      // no empty range
+    p.splits = splits;
+    p.m_rows_pad = p.m_tiles * kTileM * group;
+    p.split_stride = static_cast<int64_t>(p.m_rows_pad) * N;
+    p.out = workspace; p.out_dtype = out_dtype = HY3D_S32; p.epilogue = epilogue = HY3D_EPI_LINEAR;
+    p.act_scale = nullptr;
+  }
   p.tma_store = (out_dtype != HY3D_S32 && block_n % (geglu ? 2 * kSlabCols : kSlabCols) == 0) ? 1 : 0;
+  if (p.splits > 1) p.tma_store = 1;   // 64-byte slabs of int32 partials (block_n is a multiple of 16)
 
   // Grid and tile order.  Tiles are walked N-fastest: CTAs running together share an A tile (a
   // large activation matrix is then fetched from HBM once, while the small B stays
@@ -787,8 +958,9 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   const int sms = device_sm_count();
   if (sms <= 0) return HY3D_ERR_CUDA;
   const int total_tiles = p.m_tiles * p.n_tiles;
+  const int total_units = total_tiles * p.splits;
   const int max_clusters = sms / group;
-  int clusters = total_tiles < max_clusters ? total_tiles : max_clusters;
+  int clusters = total_units < max_clusters ? total_units : max_clusters;
   bool column_fixed = p.n_tiles == 1;
   p.n_fastest = 0;
   if (p.n_tiles > 1) {
@@ -814,7 +986,7 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
   const int ctrl_bytes = static_cast<int>(sizeof(DenseCtrl));
   const int staging1 = kEpiWarps * kSlabBytes;
   int b_resident = 0, store_bufs = 2, stages = 0, stage_bytes = 0;
-  if (group == 1 && atoms == 1 && column_fixed && total_tiles >= 2 * clusters) {
+  if (group == 1 && atoms == 1 && column_fixed && p.splits == 1 && total_tiles >= 2 * clusters) {
     // One staging buffer per epilogue warp: measured faster than two here (a warp that must
     // wait for its previous store to leave shared memory paces the store stream, and the
     // loads queue behind fewer stores).
@@ -859,7 +1031,12 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
                          static_cast<uint64_t>(K), kBlockKBytes,
                          static_cast<uint32_t>(block_n / group), 128);
   if (rc != HY3D_OK) return rc;
-  if (p.tma_store) {
+  if (p.splits > 1) {
+    const uint64_t row_bytes = static_cast<uint64_t>(N) * 4;
+    rc = encode_tmap_2d_u8(&tm_o, workspace, row_bytes, static_cast<uint64_t>(p.splits) * p.m_rows_pad,
+                           row_bytes, 64, 32, 64);
+    if (rc != HY3D_OK) return rc;
+  } else if (p.tma_store) {
     const uint64_t row_bytes = static_cast<uint64_t>(geglu ? N / 2 : N) * 2;
     rc = encode_tmap_2d_u8(&tm_o, out, row_bytes, static_cast<uint64_t>(M), row_bytes,
                            kSlabCols * 2, 32, 64);
@@ -901,11 +1078,41 @@ int gemm_dense(const int8_t* A, const int8_t* B, const float* act_scale, const v
     cudaGetLastError();
     return HY3D_ERR_CUDA;
   }
+  if (p.splits > 1) {
+    const int64_t vecs = M * (N >> 3);
+    int64_t blocks = (vecs + 255) / 256;
+    if (blocks > sms * 8) blocks = sms * 8;
+    cudaLaunchConfig_t rcfg = {};
+    rcfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    rcfg.blockDim = dim3(256);
+    rcfg.stream = stream;
+    cudaLaunchAttribute rattr[1];
+    rattr[0] = pdl_attribute();
+    rcfg.attrs = rattr;
+    rcfg.numAttrs = 1;
+    const int32_t* part = workspace;
+    uint16_t* o16 = static_cast<uint16_t*>(final_out);
+    const int Ni = static_cast<int>(N);
+    cudaError_t err;
+#define HY3D_SPLITK_REDUCE(BF, EP)                                                                    \
+  err = cudaLaunchKernelEx(&rcfg, splitk_reduce_kernel<BF, EP>, part, p.splits, p.split_stride, act_scale, \
+                           w_scale, ws_dtype, bias, bias_dtype, o16, M, Ni)
+    if (final_dtype == HY3D_BF16) {
+      if (final_epilogue == HY3D_EPI_GELU) HY3D_SPLITK_REDUCE(true, HY3D_EPI_GELU);
+      else HY3D_SPLITK_REDUCE(true, HY3D_EPI_LINEAR);
+    } else {
+      if (final_epilogue == HY3D_EPI_GELU) HY3D_SPLITK_REDUCE(false, HY3D_EPI_GELU);
+      else HY3D_SPLITK_REDUCE(false, HY3D_EPI_LINEAR);
+    }
+#undef HY3D_SPLITK_REDUCE
+    if (err != cudaSuccess) { cudaGetLastError(); return HY3D_ERR_CUDA; }
+  }
   return cudaGetLastError() == cudaSuccess ? HY3D_OK : HY3D_ERR_CUDA;
 }
 
 }  // namespace dense
 
 using dense::gemm_dense;
+using dense::dense_splitk_plan;
 
 }  // namespace hy3d

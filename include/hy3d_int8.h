@@ -148,6 +148,28 @@ int hy3d_gemm_w8a8_dense(const int8_t* A, const int8_t* B, const float* act_scal
                          int epilogue, int cta_group, int block_n, void* stream);
 
 /*
+ * Split-K form of the GEMM above for launches whose tiles leave most SMs idle while each walks
+ * a long K alone (few rows, deep K: the image encoder's M = 257, K = 6144 layer): the K blocks
+ * are cut into `splits` ranges that run side by side as int32 partials in `workspace`
+ * (splits x ceil(M/128)*128 x N x 4 bytes, 16-byte aligned, no initialisation needed), and a second kernel
+ * adds the partials -- exactly, in int32 -- and applies the epilogue with the GEMM kernel's own
+ * formula and roundings, so the result equals hy3d_gemm_w8a8_dense bit for bit.
+ * hy3d_dense_splitk_plan returns the number of ranges this library would use for a shape
+ * (1 = do not split) and the workspace it needs.  out_dtype f16/bf16, epilogue linear or GELU,
+ * N % 8 == 0; splits = 1 runs the plain kernel.
+ * Replaces: the split-K path and its reduce kernel of the reference's sparse GEMM
+ * (csrc/int8_sparse_tc.cu:1730-1732 cost terms, split-K reduce) in the dense kernel's terms.
+ */
+int hy3d_dense_splitk_plan(int64_t M, int64_t N, int64_t K, int epilogue, int64_t* workspace_bytes);
+int hy3d_gemm_w8a8_dense_splitk(const int8_t* A, const int8_t* B, const float* act_scale,
+                                const void* w_scale, int w_scale_dtype,
+                                const void* bias, int bias_dtype,
+                                void* out, int out_dtype,
+                                int64_t M, int64_t N, int64_t K,
+                                int epilogue, int splits, void* workspace, int64_t workspace_bytes,
+                                void* stream);
+
+/*
  * Whole dense linear layer: quantise x per token into the caller's workspace, then the
  * GEMM above.  x: (M,K) f16/bf16; q_ws: (M,K) int8 workspace; scale_ws: (M) f32 workspace.
  * Replaces: csrc/int8_gemm_tc.cu:312-320 (int8_linear_tc), csrc/int8_kernels.cu:193-210

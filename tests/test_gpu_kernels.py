@@ -480,3 +480,37 @@ def test_groupnorm_nhwc_argument_checks(ik):
     with pytest.raises(RuntimeError):
         ik.groupnorm_nhwc(torch.randn(1, 60, 4, 4, device=DEV).bfloat16().contiguous(memory_format=torch.channels_last),
                           32, None, None, 1e-5)                          # C % 8, C % groups
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K,N,splits,epi", [
+    (257, 6144, 1536, None, 0),     # the image encoder's deep-K layer: the library's own plan
+    (257, 6144, 1536, 5, 1),        # GELU, five ranges (48 K blocks: 10 + 10 + 10 + 10 + 8)
+    (100, 3152, 272, 3, 0),         # ragged last K block in the last range, ragged columns
+    (924, 1024, 320, 4, 0),         # two stages per range
+    (130, 4096, 64, 16, 0),         # one narrow tile column, sixteen ranges
+])
+def test_dense_splitk_equals_single_launch(tc, dtype, M, K, N, splits, epi):
+    """Split-K (int32 partials per K range + reduce/epilogue kernel) gives the bits of the
+    single-launch GEMM, whose epilogue it restates, and the int32 sums of the oracle."""
+    A, B = _rand_i8((M, K), 31).to(DEV), _rand_i8((N, K), 32).to(DEV)
+    g = torch.Generator().manual_seed(33)
+    a_s = (torch.rand(M, generator=g) * 0.05 + 1e-3).to(DEV)
+    w_s = (torch.rand(N, generator=g) * 1e-3 + 1e-5).to(dtype).to(DEV)
+    bias = (torch.randn(N, generator=g) * 0.1).to(dtype).to(DEV)
+    if splits is None:
+        planned, nbytes = tc.dense_splitk_plan(M, N, K, epi)
+        assert planned > 1 and nbytes == planned * ((M + 127) // 128 * 128) * N * 4
+    one = tc.int8_gemm_tc(A, B, a_s, w_s, bias, out_dtype=dtype, epilogue=epi, splits=1)
+    many = tc.int8_gemm_tc(A, B, a_s, w_s, bias, out_dtype=dtype, epilogue=epi, splits=splits)
+    assert torch.equal(one, many)
+    ref = O.epilogue(O.int32_matmul(A.cpu(), B.cpu()), a_s.cpu(), w_s.cpu(), bias.cpu(), dtype,
+                     "gelu" if epi else "linear")
+    assert O.rel_l2(many, ref) < 2e-3
+    assert tc.device_status() == 0
+
+
+def test_dense_splitk_plan_leaves_the_unet_shapes_alone(tc):
+    for M, K, N in [(49152, 320, 320), (12288, 640, 5120), (3072, 5120, 1280), (924, 1024, 1280)]:
+        assert tc.dense_splitk_plan(M, N, K)[0] == 1
+    assert tc.dense_splitk_plan(257, 1536, 6144)[0] > 1
